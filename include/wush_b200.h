@@ -1,0 +1,113 @@
+/*
+ * wush_b200 -- C ABI of the B200 (sm_100a) kernels for the WUSH quantized-linear hot path.
+ *
+ * Every entry point takes caller-owned DEVICE pointers plus sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t / CUstream handle; NULL is the legacy default
+ * stream).  Calls are asynchronous with respect to the host unless stated otherwise.
+ * Return value: 0 on success, a negative WUSH_ERR_* code for a rejected argument, or a
+ * positive cudaError_t value reported by the CUDA runtime for the launch.
+ *
+ * Reference interfaces are cited by their path inside the WUSH project
+ * (https://github.com/IST-DASLab/WUSH).
+ */
+#ifndef WUSH_B200_H_
+#define WUSH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define WUSH_API __attribute__((visibility("default")))
+#else
+#define WUSH_API
+#endif
+
+#define WUSH_OK 0
+#define WUSH_ERR_NULL_POINTER (-1)
+#define WUSH_ERR_BAD_SHAPE (-2)
+#define WUSH_ERR_BAD_ALIGNMENT (-3)
+#define WUSH_ERR_BAD_FLAG (-4)
+#define WUSH_ERR_WORKSPACE_TOO_SMALL (-5)
+#define WUSH_ERR_NOT_SM100 (-6)
+#define WUSH_ERR_DEVICE_TIMEOUT (-7) /* a bounded wait inside a kernel ran out; see wush_read_status */
+
+/* Layout of the per-group scale bytes written by the fused quantize kernels. */
+#define WUSH_SF_ROW_MAJOR 0 /* sf[row * sf_cols + group], sf_cols = ceil(C/G/4)*4 */
+#define WUSH_SF_BLOCKED 1   /* 128x4 tiles of 512 bytes: ((row/128)*(sf_cols/4) + group/4)*512
+                               + (row%32)*16 + ((row%128)/32)*4 + group%4 -- the layout the
+                               block-scaled tensor-core MMA consumes */
+
+/* flags of the fused quantize entry points */
+#define WUSH_QUANT_ROUND_BF16 1 /* round the transformed values to bf16 before quantizing, as the
+                                   reference's runtime module does between its einsum and its
+                                   quantizer (src/utils/wush_utils.py:140-149) */
+
+/* Library / build information: compute capability the kernels were compiled for (100). */
+WUSH_API int wush_b200_arch(void);
+
+/*
+ * Fused per-group transform + MXFP4 quantization of activations or weights.
+ *
+ * Replaces qutlass.fusedQuantizeWushMx / qutlass.fusedQuantizeMx (abs_max method) as bound at
+ * inference_lib/src/fp_quant/module/qutlass_ops.py:37-72 and :110-143, and the three-kernel
+ * pseudo-quant path of src/utils/wush_utils.py:124-150.
+ *
+ *   x        bf16 [rows, cols] row-major, cols % 32 == 0, 16-byte aligned
+ *   mat      bf16 [32, mat_cols] row-major; mat_cols == cols: column block n holds the transposed
+ *            32x32 transform of channel group n (y_n = x_n @ mat[:, 32n:32n+32]);
+ *            mat_cols == 32: one matrix shared by every group (e.g. a Hadamard matrix)
+ *   q        u8 [rows, cols/2]: E2M1 codes, element 2i in the low nibble
+ *   sf       u8 E8M0 scale bytes, one per 32 channels, in `sf_layout` with `sf_cols` bytes per
+ *            row (sf_cols % 4 == 0, sf_cols >= cols/32); only entries of real rows and groups
+ *            are written, padding is left untouched
+ * Scale = 2^floor(log2(absmax)); code = RNE_e2m1(3 * y / scale); an all-zero group gives scale
+ * byte 0 and codes 0x88.
+ */
+WUSH_API int wush_fused_quantize_mx(const void* x, const void* mat, int64_t mat_cols, uint8_t* q, uint8_t* sf,
+                           int64_t sf_cols, int sf_layout, int64_t rows, int64_t cols, int flags,
+                           void* stream);
+
+/*
+ * Fused per-group transform + NVFP4 quantization (groups of 16, E4M3 scales, fp32 tensor scale).
+ *
+ * Replaces qutlass.fusedQuantizeNv as bound at
+ * inference_lib/src/fp_quant/module/qutlass_ops.py:75-106.
+ *
+ *   mat           bf16 [16, mat_cols]; mat_cols == cols (per-group 16x16 transforms, laid out as
+ *                 above) or mat_cols == 16 (shared)
+ *   global_scale  device pointer to one fp32 (10.0 in the reference's exported checkpoints)
+ *   sf            u8 E4M3 scale bytes, one per 16 channels; sf_cols >= cols/16
+ * Scale = RN_e4m3(absmax * global_scale / 6), saturated at 448; code = RNE_e2m1(y * global_scale
+ * / scale).
+ */
+WUSH_API int wush_fused_quantize_nv(const void* x, const void* mat, int64_t mat_cols, const float* global_scale,
+                           uint8_t* q, uint8_t* sf, int64_t sf_cols, int sf_layout, int64_t rows,
+                           int64_t cols, int flags, void* stream);
+
+/*
+ * Debug/validation variant of the two calls above: same arithmetic, but also stores the
+ * transformed values (after the optional bf16 rounding) as fp32 [rows, cols].  `fmt` is 0 for
+ * MXFP4 and 1 for NVFP4 (global_scale may be NULL for MXFP4).  Used by the parity tests for the
+ * 1e-5 bound on transformed values; has no counterpart in the reference's FFI.
+ */
+WUSH_API int wush_fused_quantize_debug(int fmt, const void* x, const void* mat, int64_t mat_cols,
+                              const float* global_scale, uint8_t* q, uint8_t* sf, int64_t sf_cols,
+                              int sf_layout, float* transformed, int64_t rows, int64_t cols, int flags,
+                              void* stream);
+
+/*
+ * Row-major padded scales -> 128x4 blocked layout (see WUSH_SF_BLOCKED).
+ * Replaces qutlass.utils.to_blocked as called at
+ * inference_lib/src/fp_quant/module/qutlass_ops.py:160-161,198-199,372-373.
+ *   in   u8 [rows, cols]   out  u8, ceil(rows/128)*128 * ceil(cols/4)*4 bytes, zero in the padding
+ */
+WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, int64_t cols, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WUSH_B200_H_ */

@@ -1,0 +1,172 @@
+"""Parity of the fused transform+quantize kernel (through the C ABI) with the CPU oracle.
+
+Tolerances (stated by the task this library was built for):
+  * transformed values: 1e-5 relative, in fp32;
+  * FP4 codes and scale bytes: bit-exact except at rounding-boundary ties, at most 1e-4 of the
+    elements may differ (codes are compared with -0 folded onto +0).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import synth
+from oracle import wush_oracle as wo
+from tests.util import canon_codes, mismatch_fraction, np_u8
+
+pytestmark = pytest.mark.gpu
+
+TIE_BUDGET = 1e-4
+GROUP = {"mx": 32, "nv": 16}
+FMT = {"mx": "mxfp4", "nv": "nvfp4"}
+
+
+def _ops():
+    from wush_b200 import qutlass_ops
+    return qutlass_ops
+
+
+def _matrix(kind: str, fmt: str, cols: int) -> np.ndarray:
+    g = GROUP[fmt]
+    if kind == "hadamard":
+        return synth.hadamard_matrix(g)
+    if kind == "identity":
+        return np.eye(g)
+    return synth.wush_matrix(cols, g)
+
+
+def _run(fmt, x_bf16, mat_np, round_bf16=False, blocked=False):
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    x = x_bf16.to(dev)
+    mat = synth.to_bf16_tensor(mat_np).to(dev)
+    gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+    q, sf, tr = ops.fused_quantize_debug(x, mat, fmt, gs, round_bf16=round_bf16, sf_layout=1 if blocked else 0)
+    torch.cuda.synchronize()
+    return np_u8(q), np_u8(sf), tr.cpu().numpy().astype(np.float64)
+
+
+def _check(fmt, x_bf16, mat_np, round_bf16=False, exact=False):
+    rows, cols = x_bf16.shape
+    g = GROUP[fmt]
+    q, sf, tr = _run(fmt, x_bf16, mat_np, round_bf16)
+    x64 = synth.bf16_to_f64(x_bf16)
+    ref = wo.fused_transform_quant(x64, mat_np, FMT[fmt], round_bf16=round_bf16)
+    # transformed values, 1e-5 relative to the magnitude of the terms that were summed
+    t3 = wo.matrix_to_transform(np.abs(mat_np)) if mat_np.shape[1] != g else np.abs(mat_np).T
+    bound = wo.block_transform(np.abs(x64), t3)
+    err = np.abs(tr - ref["transformed"])
+    if round_bf16:
+        # one bf16 ulp where the fp32 and fp64 sums straddle a rounding boundary, rarely
+        assert np.mean(err > 1e-5 * bound + 1e-30) < 1e-3
+    else:
+        assert np.all(err <= 1e-5 * bound + 1e-30), float((err / (bound + 1e-30)).max())
+    # scales and codes against the oracle's own pipeline
+    sf_valid = sf[:rows, : cols // g]
+    nan_rows = np.isnan(ref["fake_quant"]).any(axis=1)
+    keep = ~nan_rows
+    f_scale = mismatch_fraction(sf_valid[keep], ref["scale_quant"][keep])
+    f_code = mismatch_fraction(canon_codes(q[keep]), canon_codes(ref["e2m1"][keep]))
+    budget = 0.0 if exact else TIE_BUDGET
+    assert f_scale <= budget, f_scale
+    assert f_code <= budget, f_code
+    # and, stricter, the oracle quantizer applied to the kernel's own transformed values: only
+    # fp32-vs-fp64 rounding of the scaled value can differ
+    ref2 = wo.rtn_xxfp4(tr, FMT[fmt])
+    keep2 = ~np.isnan(ref2["fake_quant"]).any(axis=1)
+    assert mismatch_fraction(sf_valid[keep2], ref2["scale_quant"][keep2]) <= 1e-5
+    assert mismatch_fraction(canon_codes(q[keep2]), canon_codes(ref2["e2m1"][keep2])) <= 1e-5
+    return q, sf
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+@pytest.mark.parametrize("rows,cols", [(1, 32), (16, 64), (127, 256), (129, 4096), (1024, 4096), (33, 14336)])
+@pytest.mark.parametrize("kind", ["wush", "hadamard"])
+def test_parity_random(fmt, rows, cols, kind):
+    x = synth.activations(rows, cols, seed=rows + cols)
+    _check(fmt, x, _matrix(kind, fmt, cols))
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+def test_parity_round_bf16(fmt):
+    x = synth.activations(300, 1024, seed=5)
+    _check(fmt, x, _matrix("wush", fmt, 1024), round_bf16=True)
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+def test_identity_transform_is_bit_exact(fmt, golden):
+    """With an identity matrix nothing is summed, so codes and scales must match the
+    reference-generated edge vectors exactly (ties, zeros, tiny and huge magnitudes)."""
+    g = GROUP[fmt]
+    e = torch.from_numpy(golden[f"{FMT[fmt]}_edge_in"]).to(torch.bfloat16)
+    reps = 64 // g                       # pad to 64 channels: cols must be a multiple of 32
+    x = torch.zeros(e.shape[0], 64, dtype=torch.bfloat16)
+    x[:, :g] = e
+    x[:, g:2 * g] = -e
+    del reps
+    q, sf = _check(fmt, x, np.eye(g), exact=True)
+    # all-zero groups: reference encodes scale 0 and -0 codes for MX, scale 0 and code 7 for NV
+    zero_rows = np.nonzero((x == 0).all(dim=1).numpy())[0]
+    for r in zero_rows:
+        assert (sf[r, : 64 // g] == 0).all()
+        assert (q[r] == (0x88 if fmt == "mx" else 0x77)).all()
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+def test_blocked_scale_layout(fmt):
+    rows, cols = 200, 1024 + 32 * 3
+    cols = cols // 32 * 32
+    x = synth.activations(rows, cols, seed=9)
+    mat = _matrix("hadamard", fmt, cols)
+    _, sf_rm, _ = _run(fmt, x, mat)
+    _, sf_bl, _ = _run(fmt, x, mat, blocked=True)
+    g = GROUP[fmt]
+    want = wo.to_blocked(sf_rm[:rows, : cols // g])
+    # padding is untouched by the kernel and zero-filled by the wrapper
+    assert np.array_equal(sf_bl.reshape(-1), want)
+    blk = _ops().to_blocked(torch.from_numpy(sf_rm[:rows, : cols // g].copy()).cuda())
+    assert np.array_equal(np_u8(blk).reshape(-1), want)
+
+
+def test_public_ops_shapes_and_errors():
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    x = synth.activations(130, 4096 + 64, seed=3).to(dev)
+    wm = synth.to_bf16_tensor(synth.wush_matrix(4096 + 64, 32)).to(dev)
+    q, sf, mask = ops.fused_quantize_mx_wush_op(x, wm, "abs_max", False)
+    assert q.shape == (130, (4096 + 64) // 2) and q.dtype == torch.uint8
+    assert sf.shape == (256, 132) and sf.dtype == torch.float8_e8m0fnu and mask is None
+    h = synth.to_bf16_tensor(synth.hadamard_matrix(32)).to(dev)
+    q2, sf2, mask2 = ops.fused_quantize_mx_op(x, h, "abs_max", True)
+    assert mask2.shape == (130, (4096 + 64) // 8) and bool((mask2 == 0xFF).all())
+    h16 = synth.to_bf16_tensor(synth.hadamard_matrix(16)).to(dev)
+    q3, sf3 = ops.fused_quantize_nv_op(x, h16, torch.tensor([10.0], device=dev))
+    assert sf3.shape == (256, 260) and sf3.dtype == torch.float8_e4m3fn
+    with pytest.raises(Exception):
+        ops.fused_quantize_mx_op(x.cpu(), h.cpu(), "abs_max", False)       # no CPU fallback
+    with pytest.raises(NotImplementedError):
+        ops.fused_quantize_mx_op(x, h, "quest", False)
+    empty = ops.fused_quantize_mx_op(x[:0], h, "abs_max", False)
+    assert empty[0].shape == (0, (4096 + 64) // 2)
+
+
+def test_full_size_properties():
+    """Benchmark-size run (16384 x 8192): properties that need no full oracle pass --
+    determinism, row independence (a row's codes do not depend on its neighbours) and a
+    dequantization error bound."""
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    rows, cols = 16384, 8192
+    x = synth.activations(rows, cols, seed=21).to(dev)
+    wm = synth.to_bf16_tensor(synth.wush_matrix(cols, 32)).to(dev)
+    q1, s1, _ = ops.fused_quantize_mx_wush_op(x, wm, "abs_max", False)
+    q2, s2, _ = ops.fused_quantize_mx_wush_op(x, wm, "abs_max", False)
+    assert torch.equal(q1, q2) and torch.equal(s1.view(torch.uint8), s2.view(torch.uint8))
+    idx = torch.tensor([0, 1, 127, 128, 5000, 16383], device=dev)
+    q3, s3, _ = ops.fused_quantize_mx_wush_op(x[idx].contiguous(), wm, "abs_max", False)
+    assert torch.equal(q3, q1[idx])
+    assert torch.equal(s3.view(torch.uint8)[: len(idx)], s1.view(torch.uint8)[idx])
+    # oracle on a 64-row sample
+    sample = torch.arange(0, rows, rows // 64, device=dev)[:64]
+    ref = wo.fused_transform_quant(synth.bf16_to_f64(x[sample].cpu()), wm.cpu().to(torch.float64).numpy(), "mxfp4")
+    assert mismatch_fraction(canon_codes(np_u8(q1[sample])), canon_codes(ref["e2m1"])) <= TIE_BUDGET
+    assert mismatch_fraction(np_u8(s1)[sample.cpu().numpy()][:, : cols // 32], ref["scale_quant"]) <= TIE_BUDGET

@@ -1,0 +1,178 @@
+"""Operator surface of the quantized linear layer, backed by the sm_100a library.
+
+Drop-in for ``inference_lib/src/fp_quant/module/qutlass_ops.py`` of the reference: the same
+callable names, argument meaning, output shapes/dtypes (including the 128-row / 4-column padding
+of the scale tensors) and fake (meta) implementations, so ``forward_quantize`` /
+``forward_gemm`` in ``linear_fns.py`` work unchanged when they import from here.  The torch
+custom ops live in the ``wush_b200`` namespace so that they can coexist with the reference's
+``fp_quant`` namespace in one process.
+
+Every op runs a hand-written CUDA kernel through the C ABI; a tensor that is not on a CUDA
+device, or a missing library, raises.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+HAS_QUTLASS = True  # the reference gates its real-quant path on this name
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise _lib.WushB200Error("wush_b200 ops need CUDA tensors; there is no CPU fallback")
+
+
+def _padded_scale_shape(rows: int, groups: int) -> Tuple[int, int]:
+    return (rows + 127) // 128 * 128, (groups + 3) // 4 * 4
+
+
+def _alloc_scales(rows: int, groups: int, device) -> torch.Tensor:
+    pr, pc = _padded_scale_shape(rows, groups)
+    if pr == rows and pc == groups:
+        return torch.empty(pr, pc, dtype=torch.uint8, device=device)
+    return torch.zeros(pr, pc, dtype=torch.uint8, device=device)  # the kernel skips the padding
+
+
+def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor],
+              sf_layout: int = _lib.SF_ROW_MAJOR, round_bf16: bool = False):
+    _require_cuda(x_flat, matrix, global_scale)
+    if x_flat.dim() != 2:
+        raise ValueError("x_flat must be 2-D (tokens, channels)")
+    if x_flat.dtype != torch.bfloat16 or matrix.dtype != torch.bfloat16:
+        raise ValueError("x_flat and the transform matrix must be bfloat16")
+    group = 32 if fmt == "mx" else 16
+    rows, cols = x_flat.shape
+    if cols % 32 != 0:
+        raise ValueError(f"channels ({cols}) must be a multiple of 32")
+    if matrix.dim() != 2 or matrix.shape[0] != group or matrix.shape[1] not in (group, cols):
+        raise NotImplementedError(
+            f"transform matrix of shape {tuple(matrix.shape)}: supported are ({group}, {group}) shared and "
+            f"({group}, {cols}) per-group")
+    x_flat = x_flat.contiguous()
+    matrix = matrix.contiguous()
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x_flat.device)
+    sf = _alloc_scales(rows, cols // group, x_flat.device)
+    lib = _lib.load()
+    flags = _lib.QUANT_ROUND_BF16 if round_bf16 else 0
+    with torch.cuda.device(x_flat.device):
+        if fmt == "mx":
+            rc = lib.wush_fused_quantize_mx(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], q.data_ptr(),
+                                            sf.data_ptr(), sf.shape[1], sf_layout, rows, cols, flags, _stream(x_flat))
+        else:
+            gs = global_scale.to(device=x_flat.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
+            rc = lib.wush_fused_quantize_nv(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], gs.data_ptr(),
+                                            q.data_ptr(), sf.data_ptr(), sf.shape[1], sf_layout, rows, cols, flags,
+                                            _stream(x_flat))
+    _lib.check(rc, f"wush_fused_quantize_{fmt}")
+    return q, sf
+
+
+# --------------------------------------------------------------------------------------------
+# forward quantization (reference: qutlass_ops.py:37-143)
+# --------------------------------------------------------------------------------------------
+
+@torch.library.custom_op("wush_b200::fused_quantize_mx_op", mutates_args=())
+def _fused_quantize_mx(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
+                       return_mask: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    if forward_method != "abs_max":
+        raise NotImplementedError("only forward_method='abs_max' is implemented (the method WUSH checkpoints use)")
+    q, sf = _quantize(x_flat, hadamard_matrix, "mx", None)
+    return q, sf.view(torch.float8_e8m0fnu)
+
+
+@_fused_quantize_mx.register_fake
+def _(x_flat, hadamard_matrix, forward_method, return_mask):
+    rows, groups = x_flat.size(0), x_flat.size(1) // 32
+    pr, pc = _padded_scale_shape(rows, groups)
+    return (torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device),
+            torch.empty(pr, pc, dtype=torch.float8_e8m0fnu, device=x_flat.device))
+
+
+def _all_kept_mask(x_flat: torch.Tensor) -> torch.Tensor:
+    # abs_max scaling never clips (|3x/scale| < 6), so every bit of the packed mask is set
+    return torch.full((x_flat.size(0), x_flat.size(1) // 8), 0xFF, dtype=torch.uint8, device=x_flat.device)
+
+
+def fused_quantize_mx_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
+                         return_mask: bool):
+    """(e2m1 u8 [T, C/2], e8m0 [ceil(T/128)*128, ceil(C/32/4)*4], mask | None).
+    Reference: qutlass_ops.py:37-72 (shared square transform)."""
+    q, sf = _fused_quantize_mx(x_flat, hadamard_matrix, forward_method, return_mask)
+    return q, sf, (_all_kept_mask(x_flat) if return_mask else None)
+
+
+def fused_quantize_mx_wush_op(x_flat: torch.Tensor, wush_matrix: torch.Tensor, forward_method: str,
+                              return_mask: bool):
+    """Per-group 32x32 transform given as a (32, C) matrix.  Reference: qutlass_ops.py:110-143."""
+    q, sf = _fused_quantize_mx(x_flat, wush_matrix, forward_method, return_mask)
+    return q, sf, (_all_kept_mask(x_flat) if return_mask else None)
+
+
+@torch.library.custom_op("wush_b200::fused_quantize_nv_op", mutates_args=())
+def fused_quantize_nv_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor,
+                         global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(e2m1 u8 [T, C/2], e4m3 [ceil(T/128)*128, ceil(C/16/4)*4]).  Reference: qutlass_ops.py:75-106.
+    The matrix may be (16, 16) shared or, beyond the reference, (16, C) per-group WUSH."""
+    q, sf = _quantize(x_flat, hadamard_matrix, "nv", global_scale)
+    return q, sf.view(torch.float8_e4m3fn)
+
+
+@fused_quantize_nv_op.register_fake
+def _(x_flat, hadamard_matrix, global_scale):
+    rows, groups = x_flat.size(0), x_flat.size(1) // 16
+    pr, pc = _padded_scale_shape(rows, groups)
+    return (torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device),
+            torch.empty(pr, pc, dtype=torch.float8_e4m3fn, device=x_flat.device))
+
+
+def fused_quantize_debug(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str,
+                         global_scale: Optional[torch.Tensor] = None, round_bf16: bool = False,
+                         sf_layout: int = _lib.SF_ROW_MAJOR):
+    """Validation entry: (q, sf u8, transformed fp32 [T, C]) -- the quantize kernel with its
+    transform output also written out."""
+    _require_cuda(x_flat, matrix)
+    group = 32 if fmt == "mx" else 16
+    rows, cols = x_flat.shape
+    x_flat, matrix = x_flat.contiguous(), matrix.contiguous()
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x_flat.device)
+    sf = _alloc_scales(rows, cols // group, x_flat.device)
+    tr = torch.empty(rows, cols, dtype=torch.float32, device=x_flat.device)
+    gs = None
+    if fmt == "nv":
+        gs = global_scale.to(device=x_flat.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(x_flat.device):
+        rc = lib.wush_fused_quantize_debug(0 if fmt == "mx" else 1, x_flat.data_ptr(), matrix.data_ptr(),
+                                           matrix.shape[1], gs.data_ptr() if gs is not None else None, q.data_ptr(),
+                                           sf.data_ptr(), sf.shape[1], sf_layout, tr.data_ptr(), rows, cols,
+                                           _lib.QUANT_ROUND_BF16 if round_bf16 else 0, _stream(x_flat))
+    _lib.check(rc, "wush_fused_quantize_debug")
+    return q, sf, tr
+
+
+# --------------------------------------------------------------------------------------------
+# scale layout (reference: qutlass_ops.py:372-373)
+# --------------------------------------------------------------------------------------------
+
+def to_blocked(x: torch.Tensor) -> torch.Tensor:
+    """Row-major scales (any 1-byte dtype) -> flat blocked layout, same dtype."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.element_size() != 1:
+        raise ValueError("to_blocked expects a 2-D tensor of 1-byte scales")
+    x = x.contiguous()
+    rows, cols = x.shape
+    pr, pc = _padded_scale_shape(rows, cols)
+    out = torch.empty(pr * pc, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().wush_sf_to_blocked(x.view(torch.uint8).data_ptr(), out.data_ptr(), rows, cols, _stream(x))
+    _lib.check(rc, "wush_sf_to_blocked")
+    return out.view(x.dtype)
