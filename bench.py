@@ -44,54 +44,57 @@ def measured_peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Polls SM clock and throttle reasons through NVML (read-only queries) from a thread while
+    the timed region runs; falls back to no samples when NVML is unavailable."""
 
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period, self.samples, self.mask = index, period_s, [], 0
+        self.stop = threading.Event()
+        self.max_mhz = None
+        self.thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if visible:
+                try:
+                    idx = int(visible.split(",")[self.index])
+                except ValueError:
+                    idx = self.index
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:
+            self.thread = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _poll(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.mask |= nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self.stop.set()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self) -> dict:
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0])); mx.append(float(r[1]))
-            except (ValueError, IndexError):
-                continue
-            for n, v in zip(names, r[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        top = sorted(sm)[len(sm) // 2:]            # the loaded half of the samples
-        return {"sm_mhz": sorted(top)[len(top) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for bit, n in self.REASONS.items() if self.mask & bit), "samples": len(s)}
 
 
 # ------------------------------------------------------------------------------------------
@@ -233,16 +236,18 @@ def run_ours(args) -> None:
         q_host.copy_(qd, non_blocking=True)
         sf_host.copy_(sd.view(torch.uint8)[:TOKENS, : HIDDEN // GROUP], non_blocking=True)
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = float("nan")
+    if not args.kernel_only:
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
 
     times = torch.tensor([ms, e2e_ms, kernel_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -254,7 +259,7 @@ def run_ours(args) -> None:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9
         e2e_value = world * alg * args.steps / (e2e_ms * 1e-3) / 1e9
         achieved = alg / (kernel_ms * 1e-3) / 1e9
-        cpu = cpu_quant_throughput(512, HIDDEN, repeats=2) if world == 1 else None
+        cpu = cpu_quant_throughput(512, HIDDEN, repeats=2) if (world == 1 and not args.kernel_only) else None
         if cpu:
             cpu.pop("seconds", None)
         line = {
@@ -283,7 +288,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="rows per GPU of the quantize workload")
+    ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
     args = ap.parse_args()
+    globals()["TOKENS"], globals()["HIDDEN"] = args.tokens, args.hidden
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -60,9 +60,9 @@ WUSH_API int wush_b200_arch(void);
  *   mat      bf16 [32, mat_cols] row-major; mat_cols == cols: column block n holds the transposed
  *            32x32 transform of channel group n (y_n = x_n @ mat[:, 32n:32n+32]);
  *            mat_cols == 32: one matrix shared by every group (e.g. a Hadamard matrix)
- *   q        u8 [rows, cols/2]: E2M1 codes, element 2i in the low nibble
+ *   q        u8 [rows, cols/2]: E2M1 codes, element 2i in the low nibble; 16-byte aligned
  *   sf       u8 E8M0 scale bytes, one per 32 channels, in `sf_layout` with `sf_cols` bytes per
- *            row (sf_cols % 4 == 0, sf_cols >= cols/32); only entries of real rows and groups
+ *            row (sf_cols % 4 == 0, sf_cols >= cols/32; 4-byte aligned); only entries of real rows and groups
  *            are written, padding is left untouched
  * Scale = 2^floor(log2(absmax)); code = RNE_e2m1(3 * y / scale); an all-zero group gives scale
  * byte 0 and codes 0x88.

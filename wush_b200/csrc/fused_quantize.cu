@@ -20,11 +20,16 @@
 //
 // Work split: a CTA owns a slab of 8 chunks (256 channels, 512 B per row) and a range of
 // rows; warp w owns chunk w and keeps that chunk's matrix fragments in 16 registers for the
-// CTA's lifetime.  Rows are walked 32 at a time with the next tile's loads issued before the
-// current tile's math (register double buffering).
+// CTA's lifetime.  Packed codes and scale bytes of a 32-row tile are staged in shared memory
+// and written out as full 128-byte lines (scattered 4-byte stores saturate the L1 data pipe).  Rows are walked 32 at a time; the activation loads run kStages-1 tiles ahead
+// of the math as 16-byte cp.async copies into lane-private shared-memory slots (each lane
+// reads back exactly the bytes it requested, so the ring needs no barrier and has no bank
+// conflicts), which keeps ~100 KB per SM in flight without holding registers.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 #include "../../include/wush_b200.h"
 #include "common.cuh"
@@ -51,9 +56,17 @@ struct QuantParams {
   int round_bf16;
 };
 
+__device__ __forceinline__ void mma_bf16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -64,8 +77,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // even, saturating; NaN becomes +6 (code 7).
 __device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8]) {
   uint32_t out;
-  asm volatile(
-      "{\n"
+  asm("{\n"
       ".reg .b8 b0, b1, b2, b3;\n"
       "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
       "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
@@ -80,7 +92,7 @@ __device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8]) {
 
 __device__ __forceinline__ uint32_t e4m3_byte(float v) {
   uint16_t h;
-  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(h) : "f"(0.0f), "f"(v));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(h) : "f"(0.0f), "f"(v));
   return h & 0xFFu;
 }
 
@@ -102,30 +114,29 @@ __device__ __forceinline__ int64_t sf_offset(int layout, int64_t sf_cols, int64_
 // Quantize the 8 values this lane holds for one row of one 32-channel chunk.
 //   MX: the 4 lanes of the row share one scale.  NV: lanes {0,1} and {2,3} form two groups.
 template <bool NV>
-__device__ __forceinline__ void quantize_row(float (&v)[8], float gs, int q4, uint32_t& packed,
-                                             uint32_t& scale_byte) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+__device__ __forceinline__ void quantize_row(float (&v)[8], float gs, uint32_t& packed, uint32_t& scale_byte) {
+  float amax = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                     fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   if (!NV) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   float mul;
   if (!NV) {
     // E8M0 byte of RN(0.75 * amax): the fp32 exponent field for normal amax (0.75*m with m in
     // [1,2) rounds to 1 both ways), byte 1 for a subnormal strictly above 2^-127, else 0.
-    const uint32_t bits = __float_as_uint(amax);
-    uint32_t e = bits >> 23;
-    if (e == 0) e = (amax * 0.75f > 5.877471754111438e-39f) ? 1u : 0u;
-    scale_byte = e;
+    uint32_t e = __float_as_uint(amax) >> 23;
     // multiplier 3 * 2^(127-e) = 1.5 * 2^(128-e); exact for e in 1..254
     mul = __uint_as_float(((255u - e) << 23) | 0x400000u);
-    if (e == 0 || e == 255u) {
-      // e == 0: 3 * 2^127 overflows fp32, apply it in two exact steps; e == 255: inf/NaN input
-      const float pre = (e == 0) ? 1.8446744073709552e19f : 0.0f;  // 2^64
+    if (__builtin_expect(e - 1u >= 254u, 0)) {
+      // e == 0 (zero / subnormal absmax): 3 * 2^127 overflows fp32, apply it in two exact steps;
+      // e == 255: inf/NaN input poisons the group as in the reference
+      if (e == 0) e = (amax * 0.75f > 5.877471754111438e-39f) ? 1u : 0u;
+      const float pre = (e == 0) ? 1.8446744073709552e19f : (e == 1 ? 1.0f : 0.0f);  // 2^64
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] *= pre;
-      mul = (e == 0) ? 2.7670116110564327e19f : __uint_as_float(0x7fc00000u);  // 3 * 2^63
+      mul = (e == 0) ? 2.7670116110564327e19f                                         // 3 * 2^63
+                     : (e == 1 ? __uint_as_float((254u << 23) | 0x400000u) : __uint_as_float(0x7fc00000u));
     }
+    scale_byte = e;
   } else {
     scale_byte = e4m3_byte(amax * gs / 6.0f);
     // true-division semantics of the oracle: x * gs / s; a zero scale gives inf / NaN codes
@@ -137,11 +148,45 @@ __device__ __forceinline__ void quantize_row(float (&v)[8], float gs, int q4, ui
   if (!NV && amax == 0.0f) packed = 0x88888888u;  // the reference encodes an all-zero group as -0
 }
 
-template <bool NV, bool DEBUG>
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+constexpr int kStages = 4;  // depth of the per-lane asynchronous load ring
+constexpr int kStageBytes = 4 * kWarps * 32 * 16;
+constexpr int kRingBytes = kStages * kStageBytes;
+constexpr int kMatStride = kSlab + 8;           // bf16 elements per staged matrix row (528 B: odd multiple of 16 B)
+constexpr int kMatBytes = 32 * kMatStride * 2;
+constexpr int kOutRow = 144;                    // bytes per staged output row: 128 B of codes, stride keeps STS conflict-free
+constexpr int kOutBytes = kTileRows * kOutRow;  // codes of one 32-row tile of the slab
+constexpr int kSfRow = 16;                      // staged scale bytes per row (8 MX / 16 NV used)
+constexpr int kSfBytes = kTileRows * kSfRow;
+constexpr int kQuantSmem = kRingBytes + kMatBytes + 2 * (kOutBytes + kSfBytes);
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
+// RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
+// the transformed values.
+template <bool NV, bool DEBUG, bool RB, bool BL>
 __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const QuantParams p) {
-  constexpr int TD = NV ? 16 : 32;  // transform size == quantization group
-  // matrix rows for this slab: [TD][kSlab] bf16, padded against bank conflicts
-  __shared__ __align__(16) __nv_bfloat16 smat[TD][kSlab + 8];
+  constexpr int TD = NV ? 16 : 32;       // transform size == quantization group
+  constexpr int GPC = kChunk / TD;       // scale groups per chunk
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  // [0, kRingBytes)   activation ring, lane-private 16-byte slots [stage][i][thread]
+  // then              the slab's matrices as 32 rows x (kSlab + 8) bf16, rows and columns permuted
+  //                   into MMA fragment order (see below); NVFP4 chunks are block-diagonal 32x32
+  // then              two staging buffers for a tile's packed codes and scale bytes
+  __nv_bfloat16* smat = reinterpret_cast<__nv_bfloat16*>(smem_raw + kRingBytes);
+  uint8_t* sout = smem_raw + kRingBytes + kMatBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q4 = lane & 3;
@@ -149,134 +194,225 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
   const int64_t col0 = slab_col0 + warp * kChunk;
   const bool shared_mat = p.mat_cols == TD;
 
-  // ---- stage the slab's matrices -------------------------------------------------------
-  if (shared_mat) {
-    for (int i = threadIdx.x; i < TD * TD; i += blockDim.x) smat[i / TD][i % TD] = p.mat[i];
-  } else {
-    constexpr int kVecPerRow = kSlab / 8;
-    for (int i = threadIdx.x; i < TD * kVecPerRow; i += blockDim.x) {
-      const int r = i / kVecPerRow, c = (i % kVecPerRow) * 8;
+  const int row_begin = blockIdx.y * (int)p.rows_per_cta;
+  const int row_end = min(row_begin + (int)p.rows_per_cta, (int)p.rows);
+  const int last_row = (int)p.rows - 1;
+  const int n_tiles = (row_end - row_begin + kTileRows - 1) / kTileRows;  // > 0 by construction of the grid
+  const bool active = col0 < p.cols;     // warps past the last chunk of a partial slab only help with stores
+
+  // ---- start the activation pipeline before touching the matrix ------------------------
+  const __nv_bfloat16* xcol = p.x + col0 + 8 * q4;
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t ring = smem_base + threadIdx.x * 16;
+  auto issue_tile = [&](int t) {
+    if (active && t < n_tiles) {
+      const int r0 = row_begin + t * kTileRows + g;
+      const uint32_t dst = ring + (uint32_t)(t % kStages) * kStageBytes;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = min(r0 + 8 * i, last_row);  // clamp: rows past the end are discarded later
+        cp_async_16(dst + i * (kWarps * 32 * 16), xcol + (int64_t)r * p.cols);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int t = 0; t < kStages - 1; ++t) issue_tile(t);
+
+  // ---- stage the slab's matrices in fragment order ---------------------------------------
+  // Matrix element M[k][n] of a chunk (k: input channel, n: output channel, both 0..31) goes to
+  // smem row 8*(2*ks + h) + 2*a + i for k = 8a + 4ks + 2h + i, and to column 8j + 2b + c for
+  // n = 8b + 2j + c.  An 8x8 tile (rows 8*(2ks+h).., columns 8j..) read with ldmatrix.trans
+  // then hands lane (g, q) the pair M[8q+4ks+2h+{0,1}][8(g/2)+2j+(g%2)]: exactly the B fragment
+  // of the permuted MMA described at the top of this file.
+  {
+    const int ncols = shared_mat ? TD : kSlab;
+    const int vec_per_row = ncols / 8;
+    for (int idx = threadIdx.x; idx < TD * vec_per_row; idx += blockDim.x) {
+      const int km = idx / vec_per_row;          // row of the given matrix
+      const int n8 = (idx % vec_per_row) * 8;    // first of 8 consecutive columns
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (slab_col0 + c < p.cols)
-        v = *reinterpret_cast<const uint4*>(p.mat + (int64_t)r * p.mat_cols + slab_col0 + c);
-      *reinterpret_cast<uint4*>(&smat[r][c]) = v;
+      if (shared_mat || slab_col0 + n8 < p.cols)
+        v = *reinterpret_cast<const uint4*>(p.mat + (int64_t)km * p.mat_cols + (shared_mat ? 0 : slab_col0) + n8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      // NVFP4: the 16x16 block of output group (n8/16) sits on the diagonal of the 32x32 chunk matrix
+      const int half = NV ? ((n8 >> 4) & 1) : 0;
+      const int k = km + 16 * half;
+      const int srow = 8 * (2 * ((k >> 2) & 1) + ((k >> 1) & 1)) + 2 * (k >> 3) + (k & 1);
+      const int chunk_col0 = NV && shared_mat ? 0 : (n8 & ~31);  // column base of the chunk inside smat
+      const int nb = NV && shared_mat ? n8 : (n8 & 31);          // first n inside the chunk (0, 8, 16, 24)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {              // w[j] holds n = nb + 2j + {0,1}
+        const int scol = chunk_col0 + 8 * j + 2 * (nb >> 3);
+        if (NV && shared_mat) {
+          // one shared 16x16 matrix serves both diagonal blocks of the chunk
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            const int kk = km + 16 * blk;
+            const int sr = 8 * (2 * ((kk >> 2) & 1) + ((kk >> 1) & 1)) + 2 * (kk >> 3) + (kk & 1);
+            const int sc = 8 * j + 2 * ((nb + 16 * blk) >> 3);
+            *reinterpret_cast<uint32_t*>(&smat[sr * kMatStride + sc]) = w[j];
+            const int kz = km + 16 * (1 - blk);
+            const int srz = 8 * (2 * ((kz >> 2) & 1) + ((kz >> 1) & 1)) + 2 * (kz >> 3) + (kz & 1);
+            *reinterpret_cast<uint32_t*>(&smat[srz * kMatStride + sc]) = 0u;
+          }
+        } else {
+          *reinterpret_cast<uint32_t*>(&smat[srow * kMatStride + scol]) = w[j];
+          if (NV) {
+            const int kz = km + 16 * (1 - half);
+            const int srz = 8 * (2 * ((kz >> 2) & 1) + ((kz >> 1) & 1)) + 2 * (kz >> 3) + (kz & 1);
+            *reinterpret_cast<uint32_t*>(&smat[srz * kMatStride + scol]) = 0u;
+          }
+        }
+      }
     }
   }
   __syncthreads();
-  if (col0 >= p.cols) return;
 
-  // ---- this lane's matrix fragments ----------------------------------------------------
-  // n-tile j, k-step ks: b0 = M[8q+4ks+{0,1}][n], b1 = M[8q+4ks+{2,3}][n], n = 8(g/2)+2j+(g%2)
+  // ---- this lane's matrix fragments: bfrag[j][ks][h] ---------------------------------------
   uint32_t bfrag[4][2][2];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int n = 8 * (g >> 1) + 2 * j + (g & 1);
+  {
+    const int cbase = shared_mat ? 0 : warp * kChunk;
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int k = 8 * q4 + 4 * ks + 2 * h;
-        __nv_bfloat16 lo, hi;
-        if (NV) {
-          // block-diagonal: chunk channel k pairs with outputs of the same 16-group only
-          const bool same = (k >> 4) == (n >> 4);
-          const int cb = shared_mat ? (n & 15) : warp * kChunk + n;
-          lo = same ? smat[k & 15][cb] : __float2bfloat16(0.0f);
-          hi = same ? smat[(k + 1) & 15][cb] : __float2bfloat16(0.0f);
-        } else {
-          const int cb = shared_mat ? n : warp * kChunk + n;
-          lo = smat[k][cb];
-          hi = smat[k + 1][cb];
-        }
-        bfrag[j][ks][h] = (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+        uint32_t r[4];
+        const int srow = 8 * (2 * ks + h) + (lane & 7);
+        const int scol = cbase + 8 * (lane >> 3);
+        ldmatrix_x4_trans(r, smem_base + kRingBytes + (srow * kMatStride + scol) * 2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bfrag[j][ks][h] = r[j];
       }
     }
   }
 
   const float gs = NV ? *p.global_scale : 0.0f;
-  const int64_t row_begin = (int64_t)blockIdx.y * p.rows_per_cta;
-  const int64_t row_end = min(row_begin + p.rows_per_cta, p.rows);
-  if (row_begin >= row_end) return;
-  const int64_t last_row = p.rows - 1;
-  const __nv_bfloat16* xcol = p.x + col0 + 8 * q4;
+  float* tp = DEBUG ? p.transformed + (int64_t)(row_begin + g) * p.cols + col0 + 8 * q4 : nullptr;
+  const int64_t q_stride = p.cols >> 1;
+  // store phase: thread t writes 16 bytes of codes of row t/8, segment t%8 (= chunk) of the slab
+  const int st_row = threadIdx.x >> 3, st_seg = threadIdx.x & 7;
+  const bool st_ok = slab_col0 + st_seg * kChunk < p.cols;
+  uint8_t* q_dst = p.q + (int64_t)(row_begin + st_row) * q_stride + (slab_col0 >> 1) + st_seg * 16;
+  const int sf_slab0 = (int)(slab_col0 / TD);           // first scale group of the slab
+  const int sf_total = (int)(p.cols / TD);
 
-  auto load_tile = [&](int64_t r0, uint4 (&a)[4]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int64_t r = min(r0 + g + 8 * i, last_row);  // clamp: rows past the end are discarded
-      a[i] = ld_nc_v4(xcol + r * p.cols);
-    }
-  };
+  for (int t = 0; t < n_tiles; ++t) {
+    issue_tile(t + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    const int r0 = row_begin + t * kTileRows;
+    uint8_t* out_q = sout + (t & 1) * (kOutBytes + kSfBytes);
+    uint8_t* out_sf = out_q + kOutBytes;
 
-  uint4 cur[4], nxt[4];
-  load_tile(row_begin, cur);
-  for (int64_t r0 = row_begin; r0 < row_end; r0 += kTileRows) {
-    const int64_t rn = r0 + kTileRows;
-    if (rn < row_end) load_tile(rn, nxt);
-
+    if (active) {
+      uint4 cur[4];
+      {
+        const uint4* src = reinterpret_cast<const uint4*>(smem_raw + (t % kStages) * kStageBytes) + threadIdx.x;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {  // two 16-row MMA tiles: rows g+16mt and g+8+16mt
-      const uint4 lo = cur[2 * mt], hi = cur[2 * mt + 1];
-      float acc[4][4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-        mma_bf16_16816(acc[j], lo.x, hi.x, lo.y, hi.y, bfrag[j][0][0], bfrag[j][0][1]);
-        mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, bfrag[j][1][0], bfrag[j][1][1]);
+        for (int i = 0; i < 4; ++i) cur[i] = src[i * (kWarps * 32)];
       }
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int64_t row = r0 + g + 8 * half + 16 * mt;
-        float v[8];
+      for (int mt = 0; mt < 2; ++mt) {  // two 16-row MMA tiles: rows g+16mt and g+8+16mt
+        const uint4 lo = cur[2 * mt], hi = cur[2 * mt + 1];
+        float acc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          v[2 * j] = acc[j][2 * half];
-          v[2 * j + 1] = acc[j][2 * half + 1];
+          mma_bf16_16816_zero(acc[j], lo.x, hi.x, lo.y, hi.y, bfrag[j][0][0], bfrag[j][0][1]);
+          mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, bfrag[j][1][0], bfrag[j][1][1]);
         }
-        if (p.round_bf16) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = bf16_round(v[i]);
-        }
-        if (DEBUG && row < row_end) {
-          float* t = p.transformed + row * p.cols + col0 + 8 * q4;
-          *reinterpret_cast<float4*>(t) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(t + 4) = make_float4(v[4], v[5], v[6], v[7]);
-        }
-        uint32_t packed, sbyte;
-        quantize_row<NV>(v, gs, q4, packed, sbyte);
-        if (row < row_end) {
-          *reinterpret_cast<uint32_t*>(p.q + row * (p.cols >> 1) + (col0 >> 1) + 4 * q4) = packed;
+        for (int half = 0; half < 2; ++half) {
+          const int trow = g + 8 * (half + 2 * mt);  // row inside the tile
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[2 * j] = acc[j][2 * half];
+            v[2 * j + 1] = acc[j][2 * half + 1];
+          }
+          if (RB) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = bf16_round(v[i]);
+          }
+          if (DEBUG && r0 + trow < row_end) {
+            float* t4 = tp + (int64_t)(t * kTileRows + trow - g) * p.cols;
+            *reinterpret_cast<float4*>(t4) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(t4 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          }
+          uint32_t packed, sbyte;
+          quantize_row<NV>(v, gs, packed, sbyte);
+          *reinterpret_cast<uint32_t*>(out_q + trow * kOutRow + warp * 16 + q4 * 4) = packed;
           if (NV) {
-            if ((q4 & 1) == 0) p.sf[sf_offset(p.sf_layout, p.sf_cols, row, (col0 >> 4) + (q4 >> 1))] = (uint8_t)sbyte;
+            if ((q4 & 1) == 0) out_sf[trow * kSfRow + warp * 2 + (q4 >> 1)] = (uint8_t)sbyte;
           } else {
-            if (q4 == 0) p.sf[sf_offset(p.sf_layout, p.sf_cols, row, col0 >> 5)] = (uint8_t)sbyte;
+            if (q4 == 0) out_sf[trow * kSfRow + warp] = (uint8_t)sbyte;
           }
         }
       }
     }
+    __syncthreads();  // the tile's codes and scales are staged (buffers alternate, one barrier per tile)
+
+    // ---- coalesced stores: each row of the slab is 128 contiguous bytes of codes ------------
+    if (st_ok && r0 + st_row < row_end) {
+      const uint4 v = *reinterpret_cast<const uint4*>(out_q + st_row * kOutRow + st_seg * 16);
+      *reinterpret_cast<uint4*>(q_dst + (int64_t)t * kTileRows * q_stride) = v;
+    }
+    if (warp == 0) {
+      const int row = r0 + lane;
+      if (row < row_end) {
+        constexpr int NG = kWarps * GPC;          // scale groups per slab row: 8 (MX) or 16 (NV)
+        const uint32_t* sv = reinterpret_cast<const uint32_t*>(out_sf + lane * kSfRow);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+        for (int c = 0; c < NG / 4; ++c) {        // 4 consecutive groups = one 32-bit word
+          const int grp = sf_slab0 + 4 * c;
+          if (grp >= sf_total) break;
+          const uint32_t word = sv[c];
+          uint8_t* dst;
+          if (BL) {
+            dst = p.sf + ((int64_t)(row >> 7) * (p.sf_cols >> 2) + (grp >> 2)) * 512 + (row & 31) * 16 +
+                  ((row >> 5) & 3) * 4;
+          } else {
+            dst = p.sf + (int64_t)row * p.sf_cols + grp;
+          }
+          if (grp + 4 <= sf_total) {
+            *reinterpret_cast<uint32_t*>(dst) = word;
+          } else {
+            for (int b = 0; grp + b < sf_total; ++b) dst[b] = (uint8_t)(word >> (8 * b));
+          }
+        }
+      }
+    }
   }
 }
 
-template <bool NV, bool DEBUG>
-static int launch_quant(QuantParams p, cudaStream_t stream) {
+template <bool NV, bool DEBUG, bool RB, bool BL>
+static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
-  // enough CTAs for about four co-resident waves of 2 CTAs/SM, rows in multiples of the tile
   static const int ctas_per_sm = env_int("WUSH_B200_QUANT_CTAS_PER_SM", 8);
   const int sms = sm_count();
   int64_t want_y = ((int64_t)ctas_per_sm * sms + slabs - 1) / slabs;
   int64_t rpc = (p.rows + want_y - 1) / want_y;
   rpc = ((rpc + kTileRows - 1) / kTileRows) * kTileRows;
   if (rpc < kTileRows) rpc = kTileRows;
+  if ((p.rows + rpc - 1) / rpc > 65535) rpc = ((p.rows + 65534) / 65535 + kTileRows - 1) / kTileRows * kTileRows;
   p.rows_per_cta = rpc;
-  const int64_t gy = (p.rows + rpc - 1) / rpc;
-  if (gy > 65535) {
-    p.rows_per_cta = ((p.rows + 65534) / 65535 + kTileRows - 1) / kTileRows * kTileRows;
+  dim3 grid((unsigned)slabs, (unsigned)((p.rows + rpc - 1) / rpc));
+  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL>;
+  constexpr int smem = kQuantSmem;
+  static bool attr_set = false;  // per instantiation; the attribute is per function and idempotent
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
   }
-  dim3 grid((unsigned)slabs, (unsigned)((p.rows + p.rows_per_cta - 1) / p.rows_per_cta));
-  fused_quantize_kernel<NV, DEBUG><<<grid, kWarps * 32, 0, stream>>>(p);
+  kern<<<grid, kWarps * 32, smem, stream>>>(p);
   return (int)cudaGetLastError();
+}
+
+template <bool NV, bool DEBUG>
+static int launch_quant(const QuantParams& p, cudaStream_t stream) {
+  const bool rb = p.round_bf16 != 0, bl = p.sf_layout == WUSH_SF_BLOCKED;
+  if (rb) return bl ? launch_quant_t<NV, DEBUG, true, true>(p, stream) : launch_quant_t<NV, DEBUG, true, false>(p, stream);
+  return bl ? launch_quant_t<NV, DEBUG, false, true>(p, stream) : launch_quant_t<NV, DEBUG, false, false>(p, stream);
 }
 
 static int check_quant_args(bool nv, const void* x, const void* mat, int64_t mat_cols, const float* gs,
@@ -289,7 +425,7 @@ static int check_quant_args(bool nv, const void* x, const void* mat, int64_t mat
   if (sf_cols % 4 != 0 || sf_cols < cols / g) return WUSH_ERR_BAD_SHAPE;
   if (sf_layout != WUSH_SF_ROW_MAJOR && sf_layout != WUSH_SF_BLOCKED) return WUSH_ERR_BAD_FLAG;
   if (flags & ~WUSH_QUANT_ROUND_BF16) return WUSH_ERR_BAD_FLAG;
-  if (((uintptr_t)x & 15) || ((uintptr_t)q & 3)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (((uintptr_t)x & 15) || ((uintptr_t)q & 15) || ((uintptr_t)sf & 3)) return WUSH_ERR_BAD_ALIGNMENT;
   if (mat_cols == cols && ((uintptr_t)mat & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   return WUSH_OK;
 }

@@ -62,6 +62,8 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
     q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x_flat.device)
     sf = _alloc_scales(rows, cols // group, x_flat.device)
     lib = _lib.load()
+    if rows == 0:
+        return q, sf
     flags = _lib.QUANT_ROUND_BF16 if round_bf16 else 0
     with torch.cuda.device(x_flat.device):
         if fmt == "mx":
