@@ -10,7 +10,7 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libwush_b200.so")
+LIB_PATH = os.environ.get("WUSH_B200_LIB") or os.path.join(HERE, "libwush_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "wush_b200.h")
 
 ERRORS = {

@@ -8,15 +8,11 @@
 //
 // The contraction needs 2*32 flop per element (about 165 TFLOP/s at HBM speed), which is
 // beyond the fp32 pipes but a small fraction of the tensor pipes, so the kernel uses
-// warp-level bf16 MMAs with operand fragments held in registers.  Two index permutations
-// make every global access a full 16-byte vector:
-//   * contraction index: lane q (= lane % 4) of a fragment row loads channels 8q..8q+7 of
-//     the chunk with one 16-byte load and feeds them to the MMA's k slots
-//     {2q, 2q+1, 2q+8, 2q+9} of two consecutive k-steps; the matrix fragments use the same
-//     permutation, so the product is unchanged;
-//   * output index: column 2q+i of n-tile j is assigned to output channel 8q+2j+i, so lane
-//     q ends up owning output channels 8q..8q+7 of the chunk -- 4 packed bytes, and the 4
-//     lanes of a row own the chunk's 16 contiguous bytes.
+// warp-level bf16 MMAs.  Activations travel global -> shared (16-byte cp.async) -> registers
+// (ldmatrix); the matrix fragments stay in registers.  One index permutation keeps the packing
+// cheap: column 2q+i of n-tile j is assigned to output channel 8q+2j+i, so lane q (= lane % 4)
+// ends up owning output channels 8q..8q+7 of the chunk -- 4 packed bytes, and the 4 lanes of a
+// row own the chunk's 16 contiguous bytes.
 //
 // Work split: a CTA owns a slab of 8 chunks (256 channels, 512 B per row) and a range of
 // rows; warp w owns chunk w and keeps that chunk's matrix fragments in 16 registers for the
@@ -52,7 +48,7 @@ struct QuantParams {
   int64_t sf_cols;
   int sf_layout;
   int64_t rows, cols;
-  int64_t rows_per_cta;
+  int row_splits;                   // grid.y: CTAs sharing the rows of one slab
   int round_bf16;
 };
 
@@ -114,7 +110,8 @@ __device__ __forceinline__ int64_t sf_offset(int layout, int64_t sf_cols, int64_
 // Quantize the 8 values this lane holds for one row of one 32-channel chunk.
 //   MX: the 4 lanes of the row share one scale.  NV: lanes {0,1} and {2,3} form two groups.
 template <bool NV>
-__device__ __forceinline__ void quantize_row(float (&v)[8], float gs, uint32_t& packed, uint32_t& scale_byte) {
+__device__ __forceinline__ void quantize_row(float (&v)[8], float gs, float gs6, uint32_t& packed,
+                                             uint32_t& scale_byte) {
   float amax = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
                      fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -138,9 +135,13 @@ __device__ __forceinline__ void quantize_row(float (&v)[8], float gs, uint32_t& 
     }
     scale_byte = e;
   } else {
-    scale_byte = e4m3_byte(amax * gs / 6.0f);
-    // true-division semantics of the oracle: x * gs / s; a zero scale gives inf / NaN codes
-    mul = gs / e4m3_value(scale_byte);
+    // gs6 = global_scale / 6 rounded once; the product differs from the oracle's float64
+    // absmax * gs / 6 by one fp32 rounding, which can move the E4M3 byte only within ~1e-7
+    // (relative) of a rounding boundary
+    scale_byte = e4m3_byte(amax * gs6);
+    // the oracle divides (x * gs / s); multiplying by the approximate quotient differs by two
+    // ulp at most.  A zero scale gives inf, hence +-6 / NaN codes, as the oracle's division does.
+    mul = __fdividef(gs, e4m3_value(scale_byte));
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] *= mul;
@@ -157,7 +158,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-constexpr int kStages = 4;  // depth of the per-lane asynchronous load ring
+#ifndef WUSH_Q_STAGES
+#define WUSH_Q_STAGES 3
+#endif
+#ifndef WUSH_Q_MINBLOCKS
+#define WUSH_Q_MINBLOCKS 3
+#endif
+constexpr int kStages = WUSH_Q_STAGES;  // depth of the asynchronous activation ring (tiles)
 constexpr int kStageBytes = 4 * kWarps * 32 * 16;
 constexpr int kRingBytes = kStages * kStageBytes;
 constexpr int kMatStride = kSlab + 8;           // bf16 elements per staged matrix row (528 B: odd multiple of 16 B)
@@ -174,14 +181,21 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sme
                : "r"(smem_addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
 // RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
 // the transformed values.
 template <bool NV, bool DEBUG, bool RB, bool BL>
-__global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
   constexpr int TD = NV ? 16 : 32;       // transform size == quantization group
   constexpr int GPC = kChunk / TD;       // scale groups per chunk
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  // [0, kRingBytes)   activation ring, lane-private 16-byte slots [stage][i][thread]
+  // [0, kRingBytes)   activation ring: per stage and warp a 32-row x 64-byte tile of the warp's chunk, the
+  //                   16-byte pieces of a row XOR-swizzled by (row/2)%4 so ldmatrix reads without conflicts
   // then              the slab's matrices as 32 rows x (kSlab + 8) bf16, rows and columns permuted
   //                   into MMA fragment order (see below); NVFP4 chunks are block-diagonal 32x32
   // then              two staging buffers for a tile's packed codes and scale bytes
@@ -194,24 +208,29 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
   const int64_t col0 = slab_col0 + warp * kChunk;
   const bool shared_mat = p.mat_cols == TD;
 
-  const int row_begin = blockIdx.y * (int)p.rows_per_cta;
-  const int row_end = min(row_begin + (int)p.rows_per_cta, (int)p.rows);
+  // even split of the 32-row tiles over the row splits (every split gets at least one tile)
+  const int tiles_total = (int)((p.rows + kTileRows - 1) / kTileRows);
+  const int tile_begin = (int)((int64_t)blockIdx.y * tiles_total / p.row_splits);
+  const int tile_end = (int)((int64_t)(blockIdx.y + 1) * tiles_total / p.row_splits);
+  const int row_begin = tile_begin * kTileRows;
+  const int row_end = min(tile_end * kTileRows, (int)p.rows);
   const int last_row = (int)p.rows - 1;
-  const int n_tiles = (row_end - row_begin + kTileRows - 1) / kTileRows;  // > 0 by construction of the grid
+  const int n_tiles = tile_end - tile_begin;
   const bool active = col0 < p.cols;     // warps past the last chunk of a partial slab only help with stores
 
   // ---- start the activation pipeline before touching the matrix ------------------------
   const __nv_bfloat16* xcol = p.x + col0 + 8 * q4;
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
-  const uint32_t ring = smem_base + threadIdx.x * 16;
+  // this lane copies piece q4 of rows g, g+8, g+16, g+24 of every tile
+  const uint32_t ring_wr = smem_base + warp * (kStageBytes / kWarps) + g * 64 + ((q4 ^ ((g >> 1) & 3)) << 4);
   auto issue_tile = [&](int t) {
     if (active && t < n_tiles) {
       const int r0 = row_begin + t * kTileRows + g;
-      const uint32_t dst = ring + (uint32_t)(t % kStages) * kStageBytes;
+      const uint32_t dst = ring_wr + (uint32_t)(t % kStages) * kStageBytes;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = min(r0 + 8 * i, last_row);  // clamp: rows past the end are discarded later
-        cp_async_16(dst + i * (kWarps * 32 * 16), xcol + (int64_t)r * p.cols);
+        cp_async_16(dst + i * (8 * 64), xcol + (int64_t)r * p.cols);
       }
     }
     cp_async_commit();
@@ -221,10 +240,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
 
   // ---- stage the slab's matrices in fragment order ---------------------------------------
   // Matrix element M[k][n] of a chunk (k: input channel, n: output channel, both 0..31) goes to
-  // smem row 8*(2*ks + h) + 2*a + i for k = 8a + 4ks + 2h + i, and to column 8j + 2b + c for
-  // n = 8b + 2j + c.  An 8x8 tile (rows 8*(2ks+h).., columns 8j..) read with ldmatrix.trans
-  // then hands lane (g, q) the pair M[8q+4ks+2h+{0,1}][8(g/2)+2j+(g%2)]: exactly the B fragment
-  // of the permuted MMA described at the top of this file.
+  // smem row k and column 8j + 2b + c for n = 8b + 2j + c.  An 8x8 tile (rows 16ks + 8h ..,
+  // columns 8j ..) read with ldmatrix.trans then hands lane (g, q) the pair
+  // M[16ks+8h+2q+{0,1}][8(g/2)+2j+(g%2)]: the B fragment of the column-permuted MMA described at
+  // the top of this file.
   {
     const int ncols = shared_mat ? TD : kSlab;
     const int vec_per_row = ncols / 8;
@@ -238,7 +257,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
       // NVFP4: the 16x16 block of output group (n8/16) sits on the diagonal of the 32x32 chunk matrix
       const int half = NV ? ((n8 >> 4) & 1) : 0;
       const int k = km + 16 * half;
-      const int srow = 8 * (2 * ((k >> 2) & 1) + ((k >> 1) & 1)) + 2 * (k >> 3) + (k & 1);
+      const int srow = k;
       const int chunk_col0 = NV && shared_mat ? 0 : (n8 & ~31);  // column base of the chunk inside smat
       const int nb = NV && shared_mat ? n8 : (n8 & 31);          // first n inside the chunk (0, 8, 16, 24)
 #pragma unroll
@@ -249,18 +268,18 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
 #pragma unroll
           for (int blk = 0; blk < 2; ++blk) {
             const int kk = km + 16 * blk;
-            const int sr = 8 * (2 * ((kk >> 2) & 1) + ((kk >> 1) & 1)) + 2 * (kk >> 3) + (kk & 1);
+            const int sr = kk;
             const int sc = 8 * j + 2 * ((nb + 16 * blk) >> 3);
             *reinterpret_cast<uint32_t*>(&smat[sr * kMatStride + sc]) = w[j];
             const int kz = km + 16 * (1 - blk);
-            const int srz = 8 * (2 * ((kz >> 2) & 1) + ((kz >> 1) & 1)) + 2 * (kz >> 3) + (kz & 1);
+            const int srz = kz;
             *reinterpret_cast<uint32_t*>(&smat[srz * kMatStride + sc]) = 0u;
           }
         } else {
           *reinterpret_cast<uint32_t*>(&smat[srow * kMatStride + scol]) = w[j];
           if (NV) {
             const int kz = km + 16 * (1 - half);
-            const int srz = 8 * (2 * ((kz >> 2) & 1) + ((kz >> 1) & 1)) + 2 * (kz >> 3) + (kz & 1);
+            const int srz = kz;
             *reinterpret_cast<uint32_t*>(&smat[srz * kMatStride + scol]) = 0u;
           }
         }
@@ -278,7 +297,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t r[4];
-        const int srow = 8 * (2 * ks + h) + (lane & 7);
+        const int srow = 16 * ks + 8 * h + (lane & 7);
         const int scol = cbase + 8 * (lane >> 3);
         ldmatrix_x4_trans(r, smem_base + kRingBytes + (srow * kMatStride + scol) * 2);
 #pragma unroll
@@ -288,6 +307,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
   }
 
   const float gs = NV ? *p.global_scale : 0.0f;
+  const float gs6 = gs / 6.0f;
   float* tp = DEBUG ? p.transformed + (int64_t)(row_begin + g) * p.cols + col0 + 8 * q4 : nullptr;
   const int64_t q_stride = p.cols >> 1;
   // store phase: thread t writes 16 bytes of codes of row t/8, segment t%8 (= chunk) of the slab
@@ -305,20 +325,25 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
     uint8_t* out_sf = out_q + kOutBytes;
 
     if (active) {
-      uint4 cur[4];
-      {
-        const uint4* src = reinterpret_cast<const uint4*>(smem_raw + (t % kStages) * kStageBytes) + threadIdx.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cur[i] = src[i * (kWarps * 32)];
-      }
+      __syncwarp();  // the tile was copied by all lanes of this warp
+      // A fragments: rows (lane%8) + 8*((lane/8)%2) of a 16-row tile, 16-byte piece (lane/16) + 2ks
+      const uint32_t tile = smem_base + (uint32_t)(t % kStages) * kStageBytes + warp * (kStageBytes / kWarps);
+      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {  // two 16-row MMA tiles: rows g+16mt and g+8+16mt
-        const uint4 lo = cur[2 * mt], hi = cur[2 * mt + 1];
+        uint32_t a0[4], a1[4];
+        {
+          const int r = arow + 16 * mt;
+          const uint32_t rowaddr = tile + r * 64;
+          const int sw = (r >> 1) & 3;
+          ldmatrix_x4(a0, rowaddr + ((((lane >> 4) + 0) ^ sw) << 4));
+          ldmatrix_x4(a1, rowaddr + ((((lane >> 4) + 2) ^ sw) << 4));
+        }
         float acc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          mma_bf16_16816_zero(acc[j], lo.x, hi.x, lo.y, hi.y, bfrag[j][0][0], bfrag[j][0][1]);
-          mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, bfrag[j][1][0], bfrag[j][1][1]);
+          mma_bf16_16816_zero(acc[j], a0[0], a0[1], a0[2], a0[3], bfrag[j][0][0], bfrag[j][0][1]);
+          mma_bf16_16816(acc[j], a1[0], a1[1], a1[2], a1[3], bfrag[j][1][0], bfrag[j][1][1]);
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -339,7 +364,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
             *reinterpret_cast<float4*>(t4 + 4) = make_float4(v[4], v[5], v[6], v[7]);
           }
           uint32_t packed, sbyte;
-          quantize_row<NV>(v, gs, packed, sbyte);
+          quantize_row<NV>(v, gs, gs6, packed, sbyte);
           *reinterpret_cast<uint32_t*>(out_q + trow * kOutRow + warp * 16 + q4 * 4) = packed;
           if (NV) {
             if ((q4 & 1) == 0) out_sf[trow * kSfRow + warp * 2 + (q4 >> 1)] = (uint8_t)sbyte;
@@ -384,18 +409,21 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fused_quantize_kernel(const Qu
   }
 }
 
+// Grid: x = slabs, y = row splits.  Every CTA takes an equal share (+-1) of the 32-row tiles.
+// The number of row splits is the largest that keeps all CTAs co-resident in `waves` waves of
+// (SMs x CTAs per SM), so the last wave is not a mostly empty tail.
 template <bool NV, bool DEBUG, bool RB, bool BL>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
-  static const int ctas_per_sm = env_int("WUSH_B200_QUANT_CTAS_PER_SM", 8);
-  const int sms = sm_count();
-  int64_t want_y = ((int64_t)ctas_per_sm * sms + slabs - 1) / slabs;
-  int64_t rpc = (p.rows + want_y - 1) / want_y;
-  rpc = ((rpc + kTileRows - 1) / kTileRows) * kTileRows;
-  if (rpc < kTileRows) rpc = kTileRows;
-  if ((p.rows + rpc - 1) / rpc > 65535) rpc = ((p.rows + 65534) / 65535 + kTileRows - 1) / kTileRows * kTileRows;
-  p.rows_per_cta = rpc;
-  dim3 grid((unsigned)slabs, (unsigned)((p.rows + rpc - 1) / rpc));
+  const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
+  static const int waves = env_int("WUSH_B200_QUANT_WAVES", 2);
+  const int64_t resident = (int64_t)sm_count() * WUSH_Q_MINBLOCKS;
+  int64_t splits = (resident * waves) / slabs;
+  if (splits < 1) splits = 1;
+  if (splits > tiles) splits = tiles;
+  if (splits > 65535) splits = 65535;
+  p.row_splits = (int)splits;
+  dim3 grid((unsigned)slabs, (unsigned)splits);
   auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL>;
   constexpr int smem = kQuantSmem;
   static bool attr_set = false;  // per instantiation; the attribute is per function and idempotent
