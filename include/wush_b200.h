@@ -107,6 +107,28 @@ WUSH_API int wush_fused_quantize_debug(int fmt, const void* x, const void* mat, 
  */
 WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, int64_t cols, void* stream);
 
+/* flags of wush_hessian_accumulate */
+#define WUSH_HESSIAN_LOWER_ONLY 1 /* update the lower triangle (and diagonal) only, do not mirror */
+
+/*
+ * GPTQ Hessian accumulation, in place:  H += X^T X.
+ *
+ * Replaces the Triton kernel behind accumulate_hessian(mat_hessian, mat_input, save_lower_only,
+ * compute_lower_only) at src/quantization/accumulate_hessian.py:26-148 (called from WUSH.update,
+ * src/quantization/wush_gptq.py:456-469).
+ *
+ *   h       fp32 [hidden, hidden] row-major, 16-byte aligned, read and written
+ *   x       bf16 [tokens, hidden] row-major, 16-byte aligned, hidden % 8 == 0
+ *   flags   0, or WUSH_HESSIAN_LOWER_ONLY (the reference's save_lower_only=True)
+ *   status  optional device int, set to 1 if a bounded wait inside the kernel ran out (the result
+ *           is then invalid); may be NULL
+ * bf16 products are exact in fp32 and are summed in fp32 tensor-core accumulators over the tokens
+ * of the call, then added to H with one fp32 rounding per element.  Only tiles that touch the
+ * lower triangle are computed; the upper triangle is written as a mirror image.
+ */
+WUSH_API int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
+                                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif

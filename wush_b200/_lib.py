@@ -21,6 +21,7 @@ ERRORS = {
 
 SF_ROW_MAJOR, SF_BLOCKED = 0, 1
 QUANT_ROUND_BF16 = 1
+HESSIAN_LOWER_ONLY = 1
 
 _lib = None
 
@@ -53,6 +54,7 @@ def load() -> ctypes.CDLL:
         "wush_fused_quantize_nv": [vp, vp, i64, vp, vp, vp, i64, i32, i64, i64, i32, vp],
         "wush_fused_quantize_debug": [i32, vp, vp, i64, vp, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_sf_to_blocked": [vp, vp, i64, i64, vp],
+        "wush_hessian_accumulate": [vp, vp, i64, i64, i32, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)

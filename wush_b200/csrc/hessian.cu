@@ -1,0 +1,287 @@
+// GPTQ Hessian accumulation  H += X^T X  on the sm_100a tensor cores.
+//
+// X is [tokens, hidden] bf16 row-major, H is [hidden, hidden] fp32.  Products of bf16 values are
+// exact in fp32.  The tensor core's fp32 accumulation truncates, which biases a long chain of
+// MMAs (measured: about 1.3e-5 relative after 4096 tokens), so a TMEM accumulator only ever sums
+// CHUNK = 512 tokens; the epilogue threads add the chunk results in registers with
+// round-to-nearest fp32 adds and update H in global memory once per call and element.
+//
+// Only tiles touching the lower triangle are computed (as the reference kernel does); each
+// lower element is read-modify-written once and, unless the caller wants the lower triangle
+// only, mirrored into the upper triangle.
+//
+// Structure: persistent CTAs (one per SM) walk a static list of 128 x 256 output tiles.
+//   warp 0      TMA producer: per 64-token step, 2 + 4 boxes of 64 channels x 64 tokens
+//               (128-byte swizzle) for the A (= X^T rows) and B (= X^T columns) operands
+//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16; both operands MN-major,
+//               since the contraction runs over tokens, the slow dimension of X)
+//   warps 2..9  epilogue: each thread owns one row and 128 columns of the tile in registers;
+//               per chunk TMEM -> registers (+=), after the last chunk registers -> H (+ mirror).
+//               Two 256-column TMEM accumulators alternate, so chunk c+1 is multiplied while
+//               chunk c is drained, and the H update of a tile overlaps the next tile's MMAs
+// All mbarrier waits are bounded; on expiry the CTA raises a flag, unwinds, frees its TMEM and
+// reports through the status word.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/wush_b200.h"
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace wush {
+namespace hess {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256;   // output tile
+constexpr int KT = 64;              // tokens per pipeline stage
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * KT * 2;          // 16 KB: two 64-channel boxes
+constexpr int B_BYTES = BN * KT * 2;          // 32 KB: four 64-channel boxes
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BOX_BYTES = 64 * KT * 2;        // one box: 64 channels x KT tokens
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 320;
+constexpr int CHUNK_KB = 8;                  // k-blocks (of KT tokens) summed in one TMEM accumulator: 512 tokens
+constexpr uint32_t TMEM_COLS = 512;
+
+struct Params {
+  float* h;
+  int64_t ldh;
+  int hidden;
+  int tokens;
+  int n_tiles;
+  int lower_only;   // do not mirror into the upper triangle
+  int* status;      // optional device word, set to 1 when a bounded wait ran out
+};
+
+// tile t -> (row block bi of 128, column block bj of 256); row block bi has bi/2 + 1 column blocks
+__device__ __forceinline__ void tile_coords(int t, int& bi, int& bj) {
+  int b = 0;
+  while (true) {
+    const int n = (b >> 1) + 1;
+    if (t < n) break;
+    t -= n;
+    ++b;
+  }
+  bi = b;
+  bj = t;
+}
+
+__global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
+  extern __shared__ uint8_t smem_unaligned[];
+  // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars[0..S): full, [S..2S): empty, [2S..2S+2): tmem_full, [2S+2..2S+4): tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8 * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8 * (2 * STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int k_blocks = (p.tokens + KT - 1) / KT;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ---------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&xmap);
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+        int bi, bj;
+        tile_coords(t, bi, bj);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t dst = smem_base + s * STAGE_BYTES;
+#pragma unroll
+          for (int a = 0; a < BM / 64; ++a) tma_load_2d(dst + a * BOX_BYTES, &xmap, bi * BM + 64 * a, kb * KT, full_bar(s));
+#pragma unroll
+          for (int b = 0; b < BN / 64; ++b)
+            tma_load_2d(dst + A_BYTES + b * BOX_BYTES, &xmap, bj * BN + 64 * b, kb * KT, full_bar(s));
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(1 /*bf16*/, 1, 1, BM, BN);
+      int s = 0;
+      uint32_t round = 0, it = 0;  // it counts chunks: accumulator buffer = it & 1
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+        for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += CHUNK_KB, ++it) {
+          const uint32_t buf = it & 1, use = it >> 1;
+          if (!(ok = mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int kb1 = min(kb0 + CHUNK_KB, k_blocks);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ++ks) {
+              // MN-major, 128-byte swizzle: 64-channel atoms are BOX_BYTES apart (leading offset),
+              // 8-token groups 1024 bytes apart (stride offset); 16 tokens = 2048 bytes per MMA
+              const uint64_t ad = make_smem_desc(a0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
+              const uint64_t bd = make_smem_desc(b0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
+              umma_f16(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+            }
+            umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+            if (++s == STAGES) { s = 0; ++round; }
+          }
+          if (ok) umma_commit(tfull_bar(buf));
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue ---------------------------------------------------
+    const int quarter = warp & 3;        // TMEM lanes this warp may read: 32*quarter .. +31
+    const int half = (warp - 2) >> 2;    // which 128 of the tile's 256 columns
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      int bi, bj;
+      tile_coords(t, bi, bj);
+      float acc[128];
+#pragma unroll
+      for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
+      for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += CHUNK_KB, ++it) {
+        const uint32_t buf = it & 1, use = it >> 1;
+        if (!(ok = mbar_wait(tfull_bar(buf), use & 1, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 32; ++u) acc[c * 32 + u] += __uint_as_float(r[u]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+      }
+      if (!ok) break;
+
+      // ---- H update from registers: row i, columns jh .. jh+127 -----------------------------------
+      const int i = bi * BM + quarter * 32 + lane;
+      const int jh = bj * BN + half * 128;
+      const bool row_ok = i < p.hidden;
+      float* hrow = p.h + (int64_t)i * p.ldh;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int jc = jh + c * 32;
+        if (jc > bi * BM + BM - 1) continue;  // chunk above the diagonal for every row of the tile
+        if (row_ok && jc + 31 <= i) {
+          // chunk entirely in the lower triangle of this row (and inside the matrix)
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            float4 o = *reinterpret_cast<const float4*>(hrow + jc + 4 * u);
+            o.x += acc[c * 32 + 4 * u];
+            o.y += acc[c * 32 + 4 * u + 1];
+            o.z += acc[c * 32 + 4 * u + 2];
+            o.w += acc[c * 32 + 4 * u + 3];
+            *reinterpret_cast<float4*>(hrow + jc + 4 * u) = o;
+            acc[c * 32 + 4 * u] = o.x; acc[c * 32 + 4 * u + 1] = o.y;
+            acc[c * 32 + 4 * u + 2] = o.z; acc[c * 32 + 4 * u + 3] = o.w;
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            if (row_ok && jc + u <= i) {
+              acc[c * 32 + u] += hrow[jc + u];
+              hrow[jc + u] = acc[c * 32 + u];
+            }
+          }
+        }
+        if (!p.lower_only) {
+          // mirror: element (i, j), j < i, also goes to (j, i); lanes hold consecutive i
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            const int j = jc + u;
+            if (row_ok && j < i) p.h[(int64_t)j * p.ldh + i] = acc[c * 32 + u];
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+}  // namespace hess
+}  // namespace wush
+
+using namespace wush;
+
+extern "C" int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
+                                       void* stream) {
+  if (!h || !x) return WUSH_ERR_NULL_POINTER;
+  if (tokens < 0 || hidden <= 0 || hidden % 8 != 0 || tokens > 0x7fffffff || hidden > (1 << 20)) return WUSH_ERR_BAD_SHAPE;
+  if (flags & ~WUSH_HESSIAN_LOWER_ONLY) return WUSH_ERR_BAD_FLAG;
+  if (((uintptr_t)h & 15) || ((uintptr_t)x & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (tokens == 0) return WUSH_OK;
+
+  CUtensorMap map;
+  int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
+                              (uint64_t)hidden * 2, 64, hess::KT, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != 0) return rc;
+
+  const int row_blocks = (int)((hidden + hess::BM - 1) / hess::BM);
+  int64_t n_tiles = 0;
+  for (int b = 0; b < row_blocks; ++b) n_tiles += (b >> 1) + 1;
+  // column blocks past the matrix edge never exist: bj <= bi/2 implies bj*256 <= bi*128 < hidden
+  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(hess::hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         hess::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (grid > n_tiles) grid = (int)n_tiles;
+  hess::hessian_kernel<<<grid, hess::THREADS, hess::SMEM_BYTES, (cudaStream_t)stream>>>(map, p);
+  return (int)cudaGetLastError();
+}
