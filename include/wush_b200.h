@@ -129,6 +129,35 @@ WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, i
 WUSH_API int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
                                      void* stream);
 
+/*
+ * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.
+ *
+ * Replace qutlass.matmul_mxf4_bf16_tn / qutlass.matmul_nvf4_bf16_tn as bound at
+ * inference_lib/src/fp_quant/module/qutlass_ops.py:149-168 and :187-206 (called from forward_gemm,
+ * inference_lib/src/fp_quant/module/linear_fns.py:65-76).
+ *
+ *   a, b       u8 [m, k/2], [n, k/2]: packed E2M1, element 2i in the low nibble; 16-byte aligned
+ *   sfa, sfb   scale bytes in the WUSH_SF_BLOCKED layout, covering ceil(rows/128)*128 rows and
+ *              ceil(k/G/4)*4 groups (G = 32, E8M0 for mxf4; G = 16, E4M3 for nvf4); padding entries must
+ *              hold finite scale bytes (zero is fine)
+ *   alpha      device pointer to one fp32 (1 / (weight_global_scale * act_global_scale) in the reference)
+ *   y          bf16 [m, n] row-major, 16-byte aligned; n % 8 == 0, k % 128 == 0
+ *   workspace  device scratch for split-K partial tiles (fp32 [splits, m, n]); needed only when few output
+ *              tiles exist (small m).  wush_gemm_workspace_bytes() gives the size the heuristic wants; with a
+ *              smaller (or NULL) workspace the GEMM runs unsplit.
+ *   splits     0 = choose automatically; > 0 forces that many K splits (fails if the workspace is too small)
+ *   status     optional device int set to 1 if a bounded wait inside the kernel ran out; may be NULL
+ * fp32 accumulation over the whole K range; one rounding to bf16 at the end.
+ */
+WUSH_API int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                    const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                                    size_t workspace_bytes, int splits, int* status, void* stream);
+WUSH_API int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                    const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                                    size_t workspace_bytes, int splits, int* status, void* stream);
+/* Scratch bytes the automatic split-K choice would use for this problem on the current device (0 = none). */
+WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+
 #ifdef __cplusplus
 }
 #endif

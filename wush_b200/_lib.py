@@ -55,11 +55,15 @@ def load() -> ctypes.CDLL:
         "wush_fused_quantize_debug": [i32, vp, vp, i64, vp, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_sf_to_blocked": [vp, vp, i64, i64, vp],
         "wush_hessian_accumulate": [vp, vp, i64, i64, i32, vp, vp],
+        "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
+        "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
+    lib.wush_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.wush_gemm_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib
     return lib
 

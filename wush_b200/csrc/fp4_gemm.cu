@@ -1,0 +1,401 @@
+// Block-scaled FP4 GEMM  Y[M,N] (bf16) = alpha * (A . sfa) (B . sfb)^T  for sm_100a.
+//
+// A is [M, K/2] and B is [N, K/2] packed E2M1 (two codes per byte, K contiguous: "TN");
+// the per-group scales arrive in the 128x4 blocked layout: E8M0 per 32 elements (MXFP4) or
+// E4M3 per 16 elements (NVFP4).  The products run on tcgen05.mma kind::mxf4 /
+// kind::mxf4nvf4 with block scaling: 128 x 256 output tile per CTA, K = 64 per instruction,
+// fp32 accumulation in TMEM, scale factors copied shared memory -> TMEM with tcgen05.cp.
+//
+// Persistent CTAs, one per SM:
+//   warp 0      producer: per 256-element k-block one TMA box each for A (128 rows x 128 B) and
+//               B (256 rows x 128 B), 128-byte swizzle, plus bulk copies of the scale tiles
+//   warp 1      allocates TMEM; per k-block copies the scale tiles to TMEM and issues 4 MMAs
+//   warps 2..5  epilogue: TMEM -> registers -> * alpha -> bf16 -> global (or fp32 partials when the
+//               K range is split across CTAs; a second kernel then reduces them)
+// TMEM columns: [0,256) accumulator, [256,272) scales of A, [288,320) scales of B.
+// All mbarrier waits are bounded (see sm100.cuh).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/wush_b200.h"
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace wush {
+namespace gemm {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 256;   // BK in elements = 128 bytes per row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK / 2;          // 16 KB
+constexpr int B_BYTES = BN * BK / 2;          // 32 KB
+constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4); MXFP4 uses 2
+constexpr int SFB_BYTES = 4096;               // two 128-row blocks
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SFA_COL = 256, SFB_COL = 288;
+
+struct Params {
+  const uint8_t* sfa;   // blocked scales of A: ceil(M/128) row blocks x sf_atoms_k atoms of 512 B
+  const uint8_t* sfb;
+  const float* alpha;   // device scalar
+  __nv_bfloat16* y;     // [M, N]
+  float* partial;       // [splits, M, N] when splits > 1
+  int m, n, k;
+  int m_blocks, n_blocks, k_blocks;   // k_blocks of BK elements (the last may be half)
+  int splits;           // CTAs sharing the K range of one tile
+  int sf_atoms_k;       // 512-byte atoms per 128-row block = ceil(K/group/4)
+  int sfb_row_blocks;   // 128-row blocks present in sfb
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into all four lane quarters
+__device__ __forceinline__ void sf_copy_to_tmem(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+template <bool NV>
+__device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if (NV) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  }
+}
+
+// Block-scaled instruction descriptor: E2M1 operands (format 1), both K-major, scale format
+// E8M0 (1) or E4M3 (0), K = 64, scale-factor byte offsets (0..3) inside the TMEM columns.
+__device__ __forceinline__ uint32_t make_idesc_fp4(bool nv, uint32_t sf_id) {
+  return (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((nv ? 0u : 1u) << 23) |
+         ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
+}
+
+// work item -> (m block, n block, split); m fastest so neighbouring CTAs share a weight panel
+__device__ __forceinline__ void work_coords(const Params& p, int w, int& mb, int& nb, int& sp) {
+  sp = w % p.splits;
+  const int tile = w / p.splits;
+  mb = tile % p.m_blocks;
+  nb = tile / p.m_blocks;
+}
+
+__device__ __forceinline__ void split_range(const Params& p, int sp, int& kb0, int& kb1) {
+  kb0 = (int)((int64_t)sp * p.k_blocks / p.splits);
+  kb1 = (int)((int64_t)(sp + 1) * p.k_blocks / p.splits);
+}
+
+template <bool NV>
+__global__ void __launch_bounds__(THREADS, 1)
+fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const Params p) {
+  constexpr int GROUP = NV ? 16 : 32;
+  constexpr int ATOMS = BK / GROUP / 4;            // scale atoms (128 rows x 4 scales) per k-block: 2 or 4
+  extern __shared__ uint8_t smem_unaligned[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars[0..S): full, [S..2S): empty, [2S]: tmem_full, [2S+1]: tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES), tempty_bar = bar_base + 8 * (2 * STAGES + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 4);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_work = p.m_blocks * p.n_blocks * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------- producer -------------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&amap);
+      tma_prefetch_desc(&bmap);
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        int mb, nb, sp, kb0, kb1;
+        work_coords(p, w, mb, nb, sp);
+        split_range(p, sp, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          // scale atoms really present in this k-block (the last block may hold fewer)
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
+          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES + sf_bytes * (1 + b_blocks));
+          const uint32_t dst = smem_base + s * STAGE_BYTES;
+          tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
+          tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
+          bulk_load(dst + A_BYTES + B_BYTES, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
+                    full_bar(s));
+          for (int r = 0; r < b_blocks; ++r)
+            bulk_load(dst + A_BYTES + B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
+                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, full_bar(s));
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t round = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+        int mb, nb, sp, kb0, kb1;
+        work_coords(p, w, mb, nb, sp);
+        split_range(p, sp, kb0, kb1);
+        if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
+        tc_fence_after();
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
+          const uint32_t sfa0 = b0 + B_BYTES, sfb0 = sfa0 + SFA_BYTES;
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          // scale tiles -> TMEM: atom a of A to columns SFA_COL + 4a; of B (two 128-row blocks)
+          // to SFB_COL + 8a + 4r.  Source: 32 rows of 16 bytes, 8-row groups 128 bytes apart.
+          for (int a = 0; a < atoms; ++a) {
+            sf_copy_to_tmem(tmem_base + SFA_COL + 4 * a, make_smem_desc(sfa0 + a * 512, 0, 128, kSwizzleNone));
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+              sf_copy_to_tmem(tmem_base + SFB_COL + 8 * a + 4 * r,
+                              make_smem_desc(sfb0 + r * (SFB_BYTES / 2) + a * 512, 0, 128, kSwizzleNone));
+          }
+          const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in this k-block
+          for (int ks = 0; ks < ksteps; ++ks) {
+            // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; 64 elements = 32 bytes
+            const uint64_t ad = make_smem_desc(a0 + ks * 32, 16, 1024, kSwizzle128B);
+            const uint64_t bd = make_smem_desc(b0 + ks * 32, 16, 1024, kSwizzle128B);
+            const int atom = NV ? ks : (ks >> 1);
+            const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
+            umma_fp4<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id), tmem_base + SFA_COL + 4 * atom,
+                         tmem_base + SFB_COL + 8 * atom, (kb > kb0) || (ks != 0));
+          }
+          umma_commit(empty_bar(s));
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+        if (ok) umma_commit(tfull_bar);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue ---------------------------------------------------
+    const int quarter = warp & 3;
+    const float alpha = *p.alpha;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+      int mb, nb, sp;
+      work_coords(p, w, mb, nb, sp);
+      if (!(ok = mbar_wait(tfull_bar, it & 1, abort_flag))) break;
+      tc_fence_after();
+      const int row = mb * BM + quarter * 32 + lane;
+      const int col0 = nb * BN;
+      const bool row_ok = row < p.m;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
+        tmem_ld_wait();
+        const int col = col0 + c * 32;
+        if (!row_ok || col >= p.n) continue;
+        if (p.splits == 1) {
+          __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col;
+          if (col + 32 <= p.n) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 o;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * u + 2 * v]) * alpha,
+                                                               __uint_as_float(r[8 * u + 2 * v + 1]) * alpha);
+                ow[v] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(dst + 8 * u) = o;
+            }
+          } else {
+            for (int u = 0; u < 32 && col + u < p.n; ++u) dst[u] = __float2bfloat16_rn(__uint_as_float(r[u]) * alpha);
+          }
+        } else {
+          float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col;
+          if (col + 32 <= p.n) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<float4*>(dst + 4 * u) =
+                  make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]), __uint_as_float(r[4 * u + 2]),
+                              __uint_as_float(r[4 * u + 3]));
+          } else {
+            for (int u = 0; u < 32 && col + u < p.n; ++u) dst[u] = __uint_as_float(r[u]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// Sum the per-split fp32 partial tiles, scale, round to bf16.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ alpha,
+                                     __nv_bfloat16* __restrict__ y, int64_t mn, int splits) {
+  const float a = *alpha;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < mn; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + (int64_t)s * mn + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * a, acc.y * a), hi = __floats2bfloat162_rn(acc.z * a, acc.w * a);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(y + i) = o;
+  }
+}
+
+// K splits for a problem: enough CTAs to occupy the machine when there are few output tiles
+// (small M: the GEMM streams the weights once and is HBM-bound), at least 2 k-blocks per split.
+static int choose_splits(int64_t tiles, int k_blocks, int sms) {
+  if (tiles >= sms) return 1;
+  int64_t s = sms / tiles;
+  if (s > k_blocks / 2) s = k_blocks / 2;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : (int)s;
+}
+
+static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                       const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                       size_t workspace_bytes, int force_splits, int* status, cudaStream_t stream) {
+  if (!a || !b || !sfa || !sfb || !alpha || !y) return WUSH_ERR_NULL_POINTER;
+  if (m < 0 || n <= 0 || k <= 0 || k % 128 != 0 || n % 8 != 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
+    return WUSH_ERR_BAD_SHAPE;
+  if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)sfa & 15) || ((uintptr_t)sfb & 15) || ((uintptr_t)y & 15))
+    return WUSH_ERR_BAD_ALIGNMENT;
+  if (m == 0) return WUSH_OK;
+  const int group = nv ? 16 : 32;
+  Params p{};
+  p.sfa = sfa; p.sfb = sfb; p.alpha = alpha; p.y = (__nv_bfloat16*)y;
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.m_blocks = (int)((m + BM - 1) / BM);
+  p.n_blocks = (int)((n + BN - 1) / BN);
+  p.k_blocks = (int)((k + BK - 1) / BK);
+  p.sf_atoms_k = (int)((k / group + 3) / 4);
+  p.sfb_row_blocks = (int)((n + 127) / 128);
+  p.status = status;
+  const int sms = sm_count();
+  const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
+  int splits = force_splits > 0 ? force_splits : choose_splits(tiles, p.k_blocks, sms);
+  if (splits > p.k_blocks) splits = p.k_blocks;
+  const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+  if (need > workspace_bytes || (need && !workspace)) {
+    if (force_splits > 0) return WUSH_ERR_WORKSPACE_TOO_SMALL;
+    splits = 1;   // no room for partial tiles: run unsplit
+  }
+  if (splits > 1 && ((uintptr_t)workspace & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  p.splits = splits;
+  p.partial = (float*)workspace;
+
+  CUtensorMap amap, bmap;
+  int rc = make_tensor_map_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k / 2, (uint64_t)k / 2,
+                              BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != 0) return rc;
+  rc = make_tensor_map_2d(&bmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
+                          BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != 0) return rc;
+
+  auto kern = nv ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[nv]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[nv] = true;
+  }
+  int64_t work = tiles * splits;
+  int grid = (int)(work < sms ? work : sms);
+  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(amap, bmap, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (splits > 1) {
+    const int64_t mn = m * n;   // n % 8 == 0, so rows stay 16-byte aligned and mn % 4 == 0
+    int64_t blocks = (mn / 4 + 255) / 256;
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partial, alpha, p.y, mn, splits);
+    e = cudaGetLastError();
+  }
+  return (int)e;
+}
+
+}  // namespace gemm
+}  // namespace wush
+
+extern "C" int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                      const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                                      size_t workspace_bytes, int splits, int* status, void* stream) {
+  return wush::gemm::gemm_launch(false, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
+                                 (cudaStream_t)stream);
+}
+
+extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                      const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                                      size_t workspace_bytes, int splits, int* status, void* stream) {
+  return wush::gemm::gemm_launch(true, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
+                                 (cudaStream_t)stream);
+}
+
+extern "C" size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  using namespace wush::gemm;
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int splits = choose_splits(tiles, (int)((k + BK - 1) / BK), wush::sm_count());
+  return splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+}

@@ -178,3 +178,67 @@ def to_blocked(x: torch.Tensor) -> torch.Tensor:
         rc = _lib.load().wush_sf_to_blocked(x.view(torch.uint8).data_ptr(), out.data_ptr(), rows, cols, _stream(x))
     _lib.check(rc, "wush_sf_to_blocked")
     return out.view(x.dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# GEMMs (reference: qutlass_ops.py:149-206)
+# --------------------------------------------------------------------------------------------
+
+def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor, ws_blocked: torch.Tensor,
+                       alpha: torch.Tensor, fmt: str, splits: int = 0) -> torch.Tensor:
+    """y = alpha * deq(x) @ deq(w)^T in bf16 with scales ALREADY in the blocked layout (what
+    ``to_blocked`` returns, or what the fused quantize kernel writes with ``sf_layout=SF_BLOCKED``).
+    x: (..., K/2) u8, w: (N, K/2) u8; fmt 'mx' (E8M0 per 32) or 'nv' (E4M3 per 16)."""
+    _require_cuda(x, w, xs_blocked, ws_blocked, alpha)
+    if x.dtype != torch.uint8 or w.dtype != torch.uint8:
+        raise ValueError("packed FP4 operands must be uint8")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    w = w.contiguous()
+    m, kb = x2.shape
+    n = w.shape[0]
+    if w.shape[1] != kb:
+        raise ValueError(f"K mismatch: x has {kb * 2}, w has {w.shape[1] * 2}")
+    k = kb * 2
+    group = 32 if fmt == "mx" else 16
+    need = lambda rows: (rows + 127) // 128 * 128 * ((k // group + 3) // 4 * 4)
+    if xs_blocked.numel() < need(m) or ws_blocked.numel() < need(n):
+        raise ValueError("blocked scale tensor smaller than ceil(rows/128)*128 x ceil(K/G/4)*4")
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    if m == 0:
+        return y.reshape(*lead, n)
+    lib = _lib.load()
+    al = alpha.to(device=x.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
+    with torch.cuda.device(x.device):
+        ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k)) if splits == 0 else splits * m * n * 4
+        work = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
+        fn = lib.wush_gemm_mxf4_bf16_tn if fmt == "mx" else lib.wush_gemm_nvf4_bf16_tn
+        rc = fn(x2.data_ptr(), w.data_ptr(), xs_blocked.data_ptr(), ws_blocked.data_ptr(), al.data_ptr(), y.data_ptr(),
+                m, n, k, work.data_ptr() if work is not None else None, ws_bytes, splits, None, _stream(x))
+    _lib.check(rc, f"wush_gemm_{fmt}f4_bf16_tn")
+    return y.reshape(*lead, n)
+
+
+@torch.library.custom_op("wush_b200::matmul_mxf4_bf16_tn_op", mutates_args=())
+def matmul_mxf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    """Reference: qutlass_ops.py:149-163.  xs / ws are ROW-MAJOR scales (E8M0 bytes, any 1-byte dtype) as
+    the fused quantize op returns them; they are re-laid into the blocked layout here, like the reference."""
+    return matmul_fp4_blocked(x, w, to_blocked(xs.view(torch.uint8)), to_blocked(ws.view(torch.uint8)), alpha, "mx")
+
+
+@matmul_mxf4_bf16_tn_op.register_fake
+def _(x, w, xs, ws, alpha):
+    return x.new_empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("wush_b200::matmul_nvf4_bf16_tn_op", mutates_args=())
+def matmul_nvf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    """Reference: qutlass_ops.py:187-201 (E4M3 scales per 16 elements)."""
+    return matmul_fp4_blocked(x, w, to_blocked(xs.view(torch.uint8)), to_blocked(ws.view(torch.uint8)), alpha, "nv")
+
+
+@matmul_nvf4_bf16_tn_op.register_fake
+def _(x, w, xs, ws, alpha):
+    return x.new_empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16)
