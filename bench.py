@@ -9,7 +9,9 @@ algorithmic GB/s (MXFP4, per-group WUSH matrices, 16384 tokens x 14336 channels 
 resident in HBM); `e2e` is the same pass through the public op with host buffers (pinned H2D of
 the activations and D2H of codes+scales inside the timed region).  `roofline` covers the quantize
 kernel, `cpu_baseline` times the CPU restatement of the reference's torch quantizer on a bounded
-sample.  `extra` carries the other two kernels of the path when they are built.
+sample.  `extra.gemm` (MXFP4 GEMM at 8192^3, TFLOP/s) and `extra.hessian` (262144 calibration tokens
+at hidden 4096, sharded over the GPUs with an NCCL all-reduce, tok/s) carry the other two kernels of
+the path with their own roofline and CPU-baseline objects.
 
 With --impl reference the reference's CPU path (the oracle port; the reference is pure Python
 and needs its own checkout to import) is timed on the host cores for the same workload.
@@ -49,7 +51,7 @@ class ClockSampler:
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int, period_s: float = 0.002):
+    def __init__(self, index: int, period_s: float = 0.0005):
         self.index, self.period, self.samples, self.mask = index, period_s, [], 0
         self.stop = threading.Event()
         self.max_mhz = None
@@ -165,10 +167,110 @@ def workload_config(n_gpus: int) -> dict:
 # GPU leg
 # ------------------------------------------------------------------------------------------
 
+GEMM_M = GEMM_N = GEMM_K = 8192
+HESS_TOKENS, HESS_HIDDEN = 128 * 2048, 4096
+FP4_NOMINAL_TFLOPS = 9000.0      # NVIDIA's dense FP4 figure for B200 (the 2:4-sparse figure is twice that)
+
+
+def _time_steps(fn, steps: int, torch) -> float:
+    """Average milliseconds per call, CUDA events on the launching stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
+    """MXFP4 W4A4 GEMM at 8192^3: operands produced by the fused quantize kernel from Gaussian
+    activations / N(0, 0.02^2) weights with a shared Hadamard transform, scales written directly in the
+    blocked layout."""
+    from oracle import synth
+    from wush_b200 import _lib
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(GEMM_M, GEMM_K, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    w = (torch.randn(GEMM_N, GEMM_K, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    had = synth.to_bf16_tensor(synth.hadamard_matrix(32)).to(dev)
+    xq, xs = ops._quantize(x, had, "mx", None, sf_layout=_lib.SF_BLOCKED)
+    wq, wsf = ops._quantize(w, had, "mx", None, sf_layout=_lib.SF_BLOCKED)
+    alpha = torch.tensor([1.0 / 9.0], device=dev)
+    del x, w
+    fn = lambda: ops.matmul_fp4_blocked(xq, wq, xs.view(-1), wsf.view(-1), alpha, "mx")
+    for _ in range(3):
+        fn()
+    ms = _time_steps(fn, args.steps, torch)
+    flops = 2.0 * GEMM_M * GEMM_N * GEMM_K
+    tflops = flops / (ms * 1e-3) / 1e12
+    peak4 = 4.0 * peaks["bf16_tflops"]
+    return {"metric": "mxfp4_w4a4_gemm_TFLOPS", "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms,
+            "config": {"workload": f"MXFP4 GEMM M=N=K={GEMM_M}, bf16 out, operands from the fused quantize kernel"},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "kernel": "fp4_gemm_kernel<MX>", "achieved": tflops, "peak": peak4,
+                         "unit": "TFLOP/s", "frac": tflops / peak4,
+                         "peak_kind": f"4 x {peak_kind} bf16 burst (no FP4 figure was measured)",
+                         "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None}}
+
+
+def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind) -> dict:
+    """GPTQ Hessian over 128 x 2048 calibration tokens at hidden 4096, tokens sharded over the ranks,
+    row panels all-reduced (NCCL) while the next panel is computed, then 1/N scaling + mirror."""
+    from wush_b200.hessian import DistributedHessian
+    local = HESS_TOKENS // world
+    g = torch.Generator(device=dev).manual_seed(200 + rank)
+    x = torch.randn(local, HESS_HIDDEN, generator=g, device=dev, dtype=torch.float32)
+    x[:, torch.randperm(HESS_HIDDEN, generator=torch.Generator().manual_seed(1))[: int(0.005 * HESS_HIDDEN)].to(dev)] *= 50.0
+    x = x.to(torch.bfloat16)
+
+    def job():
+        dh = DistributedHessian(HESS_HIDDEN, dev)
+        dh.accumulate_overlapped(x)
+        return dh.finalize()
+
+    steps = max(1, min(args.steps, 5))
+    for _ in range(2):
+        job()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        job()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    # kernel alone (this rank's tokens, all row panels in one launch)
+    from wush_b200 import _lib
+    lib = _lib.load()
+    h = torch.zeros(HESS_HIDDEN, HESS_HIDDEN, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    kfn = lambda: lib.wush_hessian_accumulate(h.data_ptr(), x.data_ptr(), local, HESS_HIDDEN, 1, None, st)
+    kfn()
+    kms = _time_steps(kfn, steps, torch)
+    t = torch.tensor([ms, kms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kms = (float(v) for v in t.tolist())
+    tri_flops = float(local) * HESS_HIDDEN * (HESS_HIDDEN + 1)
+    ach = tri_flops / (kms * 1e-3) / 1e12
+    return {"metric": "hessian_tokens_per_s", "value": HESS_TOKENS / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
+            "scaling": "strong", "steps": steps,
+            "config": {"workload": f"H = X^T X / N over {HESS_TOKENS} tokens (128 x 2048), hidden {HESS_HIDDEN}, bf16 "
+                                   f"in / fp32 out, {local} tokens per GPU, NCCL all-reduce of row panels"},
+            "gpu_launches": steps * 9,
+            "roofline": {"bound": "tensor", "kernel": "hessian_kernel", "achieved": ach, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "peak_kind": f"of {peak_kind} (bf16 burst)",
+                         "algorithmic_flops_per_launch": tri_flops, "kernel_ms": kms,
+                         "note": "flops of one triangle incl. diagonal, T*C*(C+1); the full-square equivalent is twice that",
+                         "traffic": None}}
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
     from oracle import synth
+    from wush_b200 import _lib
     from wush_b200 import qutlass_ops as ops
 
     rank = int(os.environ.get("RANK", "0"))
@@ -186,7 +288,10 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # inputs: every rank its own shard of rows (different seed), same matrices
+    peaks, peak_kind = measured_peaks()
+    warmup = max(args.warmup, 3)
+
+    # ---- fused transform + quantize: every rank its own shard of rows, same matrices -------------
     x_host = synth.activations(TOKENS, HIDDEN, seed=100 + rank).pin_memory()
     mat = synth.to_bf16_tensor(synth.wush_matrix(HIDDEN, GROUP)).to(dev)
     x = x_host.to(dev)
@@ -195,7 +300,7 @@ def run_ours(args) -> None:
     def step():
         return ops.fused_quantize_mx_wush_op(x, mat, "abs_max", False)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -206,38 +311,33 @@ def run_ours(args) -> None:
             step()
         ev1.record()
         barrier()
-    ms = ev0.elapsed_time(ev1)
+        ms = ev0.elapsed_time(ev1)
+
+        # kernel-only duration: events directly around the launches on the launching stream
+        lib = _lib.load()
+        q = torch.empty(TOKENS, HIDDEN // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty(TOKENS, HIDDEN // GROUP, dtype=torch.uint8, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def launch():
+            rc = lib.wush_fused_quantize_mx(x.data_ptr(), mat.data_ptr(), HIDDEN, q.data_ptr(), sf.data_ptr(),
+                                            HIDDEN // GROUP, 0, TOKENS, HIDDEN, 0, stream)
+            assert rc == 0, rc
+
+        kernel_ms = _time_steps(launch, args.steps, torch)
     clock_summary = clocks.summary()
 
-    # kernel-only duration: events directly around each launch on the launching stream
-    from wush_b200 import _lib
-    lib = _lib.load()
-    q = torch.empty(TOKENS, HIDDEN // 2, dtype=torch.uint8, device=dev)
-    sf = torch.empty(TOKENS, HIDDEN // GROUP, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream().cuda_stream
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    k0.record()
-    for _ in range(args.steps):
-        rc = lib.wush_fused_quantize_mx(x.data_ptr(), mat.data_ptr(), HIDDEN, q.data_ptr(), sf.data_ptr(),
-                                        HIDDEN // GROUP, 0, TOKENS, HIDDEN, 0, stream)
-        assert rc == 0, rc
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / args.steps
-
     # end to end: pinned host activations in, codes + scales back to pinned host memory
+    e2e_ms = float("nan")
     q_host = torch.empty(TOKENS, HIDDEN // 2, dtype=torch.uint8).pin_memory()
     sf_host = torch.empty(TOKENS, HIDDEN // GROUP, dtype=torch.uint8).pin_memory()
-
-    def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        qd, sd, _ = ops.fused_quantize_mx_wush_op(xd, mat, "abs_max", False)
-        q_host.copy_(qd, non_blocking=True)
-        sf_host.copy_(sd.view(torch.uint8)[:TOKENS, : HIDDEN // GROUP], non_blocking=True)
-
-    e2e_ms = float("nan")
     if not args.kernel_only:
+        def e2e_step():
+            xd = x_host.to(dev, non_blocking=True)
+            qd, sd, _ = ops.fused_quantize_mx_wush_op(xd, mat, "abs_max", False)
+            q_host.copy_(qd, non_blocking=True)
+            sf_host.copy_(sd.view(torch.uint8)[:TOKENS, : HIDDEN // GROUP], non_blocking=True)
+
         for _ in range(2):
             e2e_step()
         barrier()
@@ -253,33 +353,89 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms, kernel_ms = (float(v) for v in times.tolist())
+    del x, q, sf, x_host, q_host, sf_host
+
+    extra = {}
+    if not args.kernel_only:
+        gemm = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
+        hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
+        extra = {"gemm": gemm, "hessian": hess}
 
     if rank == 0:
-        peaks, peak_kind = measured_peaks()
         value = world * alg * args.steps / (ms * 1e-3) / 1e9
         e2e_value = world * alg * args.steps / (e2e_ms * 1e-3) / 1e9
         achieved = alg / (kernel_ms * 1e-3) / 1e9
-        cpu = cpu_quant_throughput(512, HIDDEN, repeats=2) if (world == 1 and not args.kernel_only) else None
-        if cpu:
+        cpu = None
+        if world == 1 and not args.kernel_only:
+            cpu = cpu_quant_throughput(512, HIDDEN, repeats=2)
             cpu.pop("seconds", None)
+            extra["gemm"]["cpu_baseline"] = cpu_gemm_throughput()
+            extra["hessian"]["cpu_baseline"] = cpu_hessian_throughput()
+        launches = args.steps + sum(v.get("gpu_launches", 0) for v in extra.values())
         line = {
             "metric": "fused_transform_quant_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": q_host.numel() + sf_host.numel(), "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": args.steps,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": TOKENS * HIDDEN * 2,
+                    "d2h_bytes_per_step": TOKENS * HIDDEN // 2 + TOKENS * HIDDEN // GROUP,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": "fused_quantize_kernel<MX>", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg,
-                         "kernel_ms": kernel_ms, "traffic": None},
+                         "kernel_ms": kernel_ms, "traffic": QUANT_TRAFFIC_BYTES_PER_LAUNCH},
             "cpu_baseline": cpu,
             "clocks": clock_summary,
+            "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM bytes per launch of the quantize kernel from the ncu capture summarised under profiles/
+# (read + write of the 8192 x 8192 case scaled by rows x channels to the benchmark shape); None until
+# a capture of the current kernel has been summarised.
+QUANT_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def cpu_gemm_throughput() -> dict:
+    """CPU restatement of the reference GEMM semantics (dequantize both operands, fp32 matmul) on a
+    bounded sample of the 8192^3 workload."""
+    import torch
+    from oracle import torch_port
+    m, n, k = 2048, 8192, GEMM_K
+    g = torch.Generator().manual_seed(3)
+    a = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8)
+    b = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    sa = torch.randint(120, 130, (m, k // 32), generator=g, dtype=torch.uint8)
+    sb = torch.randint(120, 130, (n, k // 32), generator=g, dtype=torch.uint8)
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch_port.fp4_gemm(a[:32], sa[:32], b[:32], sb[:32], 1.0, "mxfp4")
+    t0 = time.perf_counter()
+    torch_port.fp4_gemm(a, sa, b, sb, 1.0 / 9.0, "mxfp4")
+    sec = time.perf_counter() - t0
+    return {"value": 2.0 * m * n * k / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"M={m}, N={n} of the 8192^3 problem (K full), dequantize + fp32 matmul on CPU: {sec:.2f} s"}
+
+
+def cpu_hessian_throughput() -> dict:
+    """WUSH.update arithmetic on CPU (fp32, the Triton launch replaced by addmm) for a few sequences."""
+    import torch
+    from oracle import synth, torch_port
+    torch.set_num_threads(os.cpu_count() or 1)
+    seqs, tok = 25, 2048
+    xs = [synth.activations(tok, HESS_HIDDEN, seed=300 + i) for i in range(seqs)]
+    h, n = torch.zeros(HESS_HIDDEN, HESS_HIDDEN), 0
+    n = torch_port.hessian_update(h, n, xs[0][None])
+    t0 = time.perf_counter()
+    for x in xs[1:]:
+        n = torch_port.hessian_update(h, n, x[None])
+    sec = time.perf_counter() - t0
+    return {"value": (seqs - 1) * tok / sec, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{seqs - 1} of 128 sequences of {tok} tokens, hidden {HESS_HIDDEN}, fp32 running-mean update on CPU: "
+                      f"{sec:.2f} s"}
 
 
 def main() -> None:

@@ -130,6 +130,22 @@ WUSH_API int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, in
                                      void* stream);
 
 /*
+ * The same update restricted to rows [row_begin, row_end) of H (row_begin % 128 == 0; row_end % 128 == 0 or
+ * row_end == hidden).  Lets a caller finish H one row panel at a time, e.g. to all-reduce a finished panel
+ * across GPUs while the next one is being computed.  With the mirror enabled the matching columns of the
+ * upper triangle are written too.  No counterpart in the reference, which is single-GPU.
+ */
+WUSH_API int wush_hessian_accumulate_rows(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
+                                          int64_t row_end, int flags, int* status, void* stream);
+
+/*
+ * h[i][j] <- scale * h[i][j] for j <= i, and h[j][i] <- the same value: turns a lower-triangular raw sum
+ * into the symmetric running mean that WUSH.update maintains (src/quantization/wush_gptq.py:467-468 applies
+ * the 1/N factor on every call; applying it once here is algebraically the same).  hidden % 4 == 0.
+ */
+WUSH_API int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* stream);
+
+/*
  * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.
  *
  * Replace qutlass.matmul_mxf4_bf16_tn / qutlass.matmul_nvf4_bf16_tn as bound at

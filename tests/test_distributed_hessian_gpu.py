@@ -1,0 +1,62 @@
+"""Token-sharded Hessian over NCCL on 2 GPUs (skipped on a single-GPU box), and the single-GPU path of
+the same class against a float64 accumulation."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import synth
+from oracle import wush_oracle as wo
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_single_gpu_update_and_overlapped():
+    from wush_b200.hessian import DistributedHessian
+    dev = torch.device("cuda:0")
+    hidden = 640
+    xs = [synth.activations(t, hidden, seed=60 + i) for i, t in enumerate((2048, 100, 1500))]
+    want = wo.wush_update_sequence([synth.bf16_to_f64(x) for x in xs])
+    a = DistributedHessian(hidden, dev)
+    for x in xs:
+        a.update(x.to(dev)[None])
+    ha = a.finalize().double().cpu().numpy()
+    b = DistributedHessian(hidden, dev, panels=3)
+    b.accumulate_overlapped(torch.cat(xs).to(dev))
+    hb = b.finalize().double().cpu().numpy()
+    for h in (ha, hb):
+        assert np.abs(h - want).max() <= 1e-5 * np.abs(want).max()
+        assert np.array_equal(h, h.T)
+    assert a.num_samples == b.num_samples == 3648
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from wush_b200.hessian import DistributedHessian
+    x = synth.activations(1024 + 256 * rank, 1024, seed=70 + rank).to(dev)
+    dh = DistributedHessian(1024, dev, panels=4)
+    dh.accumulate_overlapped(x)
+    h = dh.finalize()
+    torch.cuda.synchronize()
+    if rank == 0:
+        np.save(out, h.cpu().numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_nccl(tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "h.npy")
+    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, out), nprocs=2, join=True)
+    got = np.load(out).astype(np.float64)
+    want = wo.wush_update_sequence([synth.bf16_to_f64(synth.activations(1024 + 256 * r, 1024, seed=70 + r)) for r in range(2)])
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()

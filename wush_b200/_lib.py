@@ -55,6 +55,8 @@ def load() -> ctypes.CDLL:
         "wush_fused_quantize_debug": [i32, vp, vp, i64, vp, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_sf_to_blocked": [vp, vp, i64, i64, vp],
         "wush_hessian_accumulate": [vp, vp, i64, i64, i32, vp, vp],
+        "wush_hessian_accumulate_rows": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
+        "wush_hessian_finalize": [vp, i64, ctypes.c_float, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
     }

@@ -52,13 +52,14 @@ struct Params {
   int hidden;
   int tokens;
   int n_tiles;
+  int first_block;  // first 128-row block of this launch (row panels can be launched separately)
   int lower_only;   // do not mirror into the upper triangle
   int* status;      // optional device word, set to 1 when a bounded wait ran out
 };
 
 // tile t -> (row block bi of 128, column block bj of 256); row block bi has bi/2 + 1 column blocks
-__device__ __forceinline__ void tile_coords(int t, int& bi, int& bj) {
-  int b = 0;
+__device__ __forceinline__ void tile_coords(int t, int first_block, int& bi, int& bj) {
+  int b = first_block;
   while (true) {
     const int n = (b >> 1) + 1;
     if (t < n) break;
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       bool ok = true;
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
         int bi, bj;
-        tile_coords(t, bi, bj);
+        tile_coords(t, p.first_block, bi, bj);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
     bool ok = true;
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       int bi, bj;
-      tile_coords(t, bi, bj);
+      tile_coords(t, p.first_block, bi, bj);
       float acc[128];
 #pragma unroll
       for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
@@ -254,24 +255,27 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
 
 using namespace wush;
 
-extern "C" int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
-                                       void* stream) {
+static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin, int64_t row_end,
+                          int flags, int* status, cudaStream_t stream) {
   if (!h || !x) return WUSH_ERR_NULL_POINTER;
   if (tokens < 0 || hidden <= 0 || hidden % 8 != 0 || tokens > 0x7fffffff || hidden > (1 << 20)) return WUSH_ERR_BAD_SHAPE;
+  if (row_begin < 0 || row_end > hidden || row_begin > row_end || row_begin % hess::BM != 0 ||
+      (row_end % hess::BM != 0 && row_end != hidden))
+    return WUSH_ERR_BAD_SHAPE;
   if (flags & ~WUSH_HESSIAN_LOWER_ONLY) return WUSH_ERR_BAD_FLAG;
   if (((uintptr_t)h & 15) || ((uintptr_t)x & 15)) return WUSH_ERR_BAD_ALIGNMENT;
-  if (tokens == 0) return WUSH_OK;
+  if (tokens == 0 || row_begin == row_end) return WUSH_OK;
 
   CUtensorMap map;
   int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
                               (uint64_t)hidden * 2, 64, hess::KT, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != 0) return rc;
 
-  const int row_blocks = (int)((hidden + hess::BM - 1) / hess::BM);
+  const int b0 = (int)(row_begin / hess::BM), b1 = (int)((row_end + hess::BM - 1) / hess::BM);
   int64_t n_tiles = 0;
-  for (int b = 0; b < row_blocks; ++b) n_tiles += (b >> 1) + 1;
+  for (int b = b0; b < b1; ++b) n_tiles += (b >> 1) + 1;
   // column blocks past the matrix edge never exist: bj <= bi/2 implies bj*256 <= bi*128 < hidden
-  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
 
   static bool attr_set = false;
   if (!attr_set) {
@@ -282,6 +286,54 @@ extern "C" int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, 
   }
   int grid = sm_count();
   if (grid > n_tiles) grid = (int)n_tiles;
-  hess::hessian_kernel<<<grid, hess::THREADS, hess::SMEM_BYTES, (cudaStream_t)stream>>>(map, p);
+  hess::hessian_kernel<<<grid, hess::THREADS, hess::SMEM_BYTES, stream>>>(map, p);
+  return (int)cudaGetLastError();
+}
+
+namespace wush {
+namespace hess {
+// Lower triangle (already summed) -> scaled lower triangle and its mirror image.  One thread per
+// 4 consecutive columns of a row; the mirrored writes are strided, the volume is 2 passes over H.
+__global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale) {
+  const int64_t quads = hidden / 4;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < hidden * quads;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = idx / quads, j0 = (idx % quads) * 4;
+    if (j0 > i) continue;
+    float4 v = *reinterpret_cast<float4*>(h + i * hidden + j0);
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    if (j0 + 3 <= i) {
+      *reinterpret_cast<float4*>(h + i * hidden + j0) = v;
+    } else {
+      for (int u = 0; u < 4; ++u)
+        if (j0 + u <= i) h[i * hidden + j0 + u] = e[u];
+    }
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u < i) h[(j0 + u) * hidden + i] = e[u];
+  }
+}
+}  // namespace hess
+}  // namespace wush
+
+extern "C" int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
+                                       void* stream) {
+  return hessian_launch(h, x, tokens, hidden, 0, hidden, flags, status, (cudaStream_t)stream);
+}
+
+extern "C" int wush_hessian_accumulate_rows(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
+                                            int64_t row_end, int flags, int* status, void* stream) {
+  return hessian_launch(h, x, tokens, hidden, row_begin, row_end, flags, status, (cudaStream_t)stream);
+}
+
+extern "C" int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* stream) {
+  if (!h) return WUSH_ERR_NULL_POINTER;
+  if (hidden <= 0 || hidden % 4 != 0) return WUSH_ERR_BAD_SHAPE;
+  if ((uintptr_t)h & 15) return WUSH_ERR_BAD_ALIGNMENT;
+  const int64_t work = hidden * (hidden / 4);
+  int64_t blocks = (work + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  hess::finalize_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, scale);
   return (int)cudaGetLastError();
 }

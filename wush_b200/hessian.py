@@ -41,3 +41,115 @@ def accumulate_hessian(mat_hessian: torch.Tensor, mat_input: torch.Tensor, save_
             rc = lib.wush_hessian_accumulate(h3[b].data_ptr(), x3[b].data_ptr(), tokens, hidden, flags, None, stream)
             _lib.check(rc, "wush_hessian_accumulate")
     return mat_hessian
+
+
+def _kernel_accumulate(h: torch.Tensor, x: torch.Tensor, row_begin: int, row_end: int, lower_only: bool) -> None:
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.wush_hessian_accumulate_rows(h.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1], row_begin, row_end,
+                                              _lib.HESSIAN_LOWER_ONLY if lower_only else 0, None,
+                                              torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "wush_hessian_accumulate_rows")
+
+
+def _kernel_finalize(h: torch.Tensor, scale: float) -> None:
+    with torch.cuda.device(h.device):
+        rc = _lib.load().wush_hessian_finalize(h.data_ptr(), h.shape[0], scale, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "wush_hessian_finalize")
+
+
+def panel_bounds(hidden: int, panels: int, align: int = 128) -> list[tuple[int, int]]:
+    """Row panels of roughly equal lower-triangle area, boundaries on multiples of `align`."""
+    cuts = [0]
+    for p in range(1, panels):
+        r = int(round(hidden * (p / panels) ** 0.5 / align)) * align
+        r = min(max(r, cuts[-1]), hidden)
+        if r > cuts[-1]:
+            cuts.append(r)
+    if cuts[-1] < hidden:
+        cuts.append(hidden)
+    return list(zip(cuts[:-1], cuts[1:]))
+
+
+class DistributedHessian:
+    """Second moment H = (1/N) sum_tokens x^T x with the calibration tokens sharded over the ranks of a
+    process group: what ``WUSH.update`` (src/quantization/wush_gptq.py:456-469) maintains on one GPU.
+
+    Each rank adds its own tokens into a raw fp32 sum (lower triangle only, bf16 inputs are not
+    rescaled per call, so their products stay exact); the ranks are combined by one all-reduce per
+    Hessian and the 1/N factor and the mirror image are applied once at the end.
+
+    ``update(x)`` mirrors the calibration hook (one sequence per call).  ``accumulate_overlapped(x)``
+    takes all local tokens at once and finishes H panel by panel, all-reducing every finished row
+    panel on a side stream while the next one is computed.
+
+    `accumulate_fn` / `finalize_fn` exist so that the host logic can be exercised on CPU ranks
+    (gloo) with a stand-in for the CUDA kernels; the defaults call the kernels and need a GPU.
+    """
+
+    def __init__(self, hidden: int, device, group=None, panels: int = 8, accumulate_fn=None, finalize_fn=None):
+        import torch.distributed as dist
+        self.hidden, self.device, self.group, self.panels = hidden, torch.device(device), group, panels
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.raw = torch.zeros(hidden, hidden, dtype=torch.float32, device=self.device)
+        self.local_tokens = 0
+        self._reduced = False
+        self._accumulate = accumulate_fn or _kernel_accumulate
+        self._finalize = finalize_fn or _kernel_finalize
+        self._comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+
+    # -- per-call path (calibration hook) ----------------------------------------------------------
+    def update(self, x: torch.Tensor) -> None:
+        x = x.reshape(-1, x.shape[-1])
+        if not x.is_contiguous():
+            x = x.contiguous()
+        assert not self._reduced, "update after the cross-rank reduction"
+        self._accumulate(self.raw, x, 0, self.hidden, True)
+        self.local_tokens += x.shape[0]
+
+    # -- all local tokens at once, reduction overlapped with compute --------------------------------
+    def accumulate_overlapped(self, x: torch.Tensor) -> None:
+        import torch.distributed as dist
+        x = x.reshape(-1, x.shape[-1])
+        assert not self._reduced
+        cuda = self._comm_stream is not None
+        for (r0, r1) in panel_bounds(self.hidden, self.panels):
+            self._accumulate(self.raw, x, r0, r1, True)
+            if self.world == 1:
+                continue
+            if cuda:
+                done = torch.cuda.Event()
+                done.record()
+                self._comm_stream.wait_event(done)
+                with torch.cuda.stream(self._comm_stream):
+                    self._reduce_panel(r0, r1)
+            else:
+                self._reduce_panel(r0, r1)
+        if cuda and self.world > 1:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+        self.local_tokens += x.shape[0]
+        self._reduced = True
+        del dist
+
+    def _reduce_panel(self, r0: int, r1: int) -> None:
+        import torch.distributed as dist
+        # only columns [0, r1) of these rows hold data: pack them so the wire carries no zeros
+        staged = self.raw[r0:r1, :r1].contiguous()
+        dist.all_reduce(staged, group=self.group)
+        self.raw[r0:r1, :r1].copy_(staged)
+
+    # -- result ---------------------------------------------------------------------------------------
+    def finalize(self) -> torch.Tensor:
+        import torch.distributed as dist
+        total = self.local_tokens
+        if self.world > 1:
+            if not self._reduced:
+                for (r0, r1) in panel_bounds(self.hidden, self.panels):
+                    self._reduce_panel(r0, r1)
+                self._reduced = True
+            n = torch.tensor([self.local_tokens], dtype=torch.int64, device=self.device)
+            dist.all_reduce(n, group=self.group)
+            total = int(n.item())
+        self._finalize(self.raw, 1.0 / max(total, 1))
+        self.num_samples = total
+        return self.raw
