@@ -214,22 +214,26 @@ def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
                          "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None}}
 
 
-def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind) -> dict:
-    """GPTQ Hessian over 128 x 2048 calibration tokens at hidden 4096, tokens sharded over the ranks,
-    row panels all-reduced (NCCL) while the next panel is computed, then 1/N scaling + mirror."""
+def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=HESS_HIDDEN) -> dict:
+    """GPTQ Hessian over 128 x 2048 calibration tokens, tokens sharded over the ranks, row panels
+    all-reduced (NCCL) while the next panel is computed, then 1/N scaling + mirror."""
     from wush_b200.hessian import DistributedHessian
     local = HESS_TOKENS // world
     g = torch.Generator(device=dev).manual_seed(200 + rank)
-    x = torch.randn(local, HESS_HIDDEN, generator=g, device=dev, dtype=torch.float32)
-    x[:, torch.randperm(HESS_HIDDEN, generator=torch.Generator().manual_seed(1))[: int(0.005 * HESS_HIDDEN)].to(dev)] *= 50.0
-    x = x.to(torch.bfloat16)
+    outl = torch.randperm(HESS_HIDDEN, generator=torch.Generator().manual_seed(1))[: int(0.005 * HESS_HIDDEN)].to(dev)
+    x = torch.empty(local, HESS_HIDDEN, device=dev, dtype=torch.bfloat16)
+    for r0 in range(0, local, 16384):          # generate in slices: the fp32 temporary stays small
+        blk = torch.randn(min(16384, local - r0), HESS_HIDDEN, generator=g, device=dev, dtype=torch.float32)
+        blk[:, outl] *= 50.0
+        x[r0:r0 + blk.shape[0]] = blk.to(torch.bfloat16)
+    del blk
 
     def job():
         dh = DistributedHessian(HESS_HIDDEN, dev)
         dh.accumulate_overlapped(x)
         return dh.finalize()
 
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, min(args.steps, 5 if HESS_HIDDEN <= 4096 else 3))
     for _ in range(2):
         job()
     barrier()
@@ -258,7 +262,7 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
             "scaling": "strong", "steps": steps,
             "config": {"workload": f"H = X^T X / N over {HESS_TOKENS} tokens (128 x 2048), hidden {HESS_HIDDEN}, bf16 "
                                    f"in / fp32 out, {local} tokens per GPU, NCCL all-reduce of row panels"},
-            "gpu_launches": steps * 9,
+            "gpu_launches": steps * (2 if world == 1 else 5),
             "roofline": {"bound": "tensor", "kernel": "hessian_kernel", "achieved": ach, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "peak_kind": f"of {peak_kind} (bf16 burst)",
                          "algorithmic_flops_per_launch": tri_flops, "kernel_ms": kms,
@@ -359,7 +363,8 @@ def run_ours(args) -> None:
     if not args.kernel_only:
         gemm = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
         hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
-        extra = {"gemm": gemm, "hessian": hess}
+        hess_ffn = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
+        extra = {"gemm": gemm, "hessian": hess, "hessian_hidden14336": hess_ffn}
 
     if rank == 0:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9

@@ -10,9 +10,11 @@
 //   warp 0      producer: per 256-element k-block one TMA box each for A (128 rows x 128 B) and
 //               B (256 rows x 128 B), 128-byte swizzle, plus bulk copies of the scale tiles
 //   warp 1      allocates TMEM; per k-block copies the scale tiles to TMEM and issues 4 MMAs
-//   warps 2..5  epilogue: TMEM -> registers -> * alpha -> bf16 -> global (or fp32 partials when the
-//               K range is split across CTAs; a second kernel then reduces them)
-// TMEM columns: [0,256) accumulator, [256,272) scales of A, [288,320) scales of B.
+//   warps 2..9  epilogue: each thread drains one row x 128 columns of the accumulator into registers,
+//               releases TMEM (the next tile's MMAs start), then * alpha -> bf16 -> global (or fp32
+//               partials when the K range is split across CTAs; a second kernel then reduces them)
+// TMEM columns: [0,256) accumulator; from 256 on, one 48-column scale region per pipeline stage
+// (16 for A, 32 for B), so a stage's scale copy never waits for the previous stage's MMAs.
 // All mbarrier waits are bounded (see sm100.cuh).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -35,9 +37,9 @@ constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4);
 constexpr int SFB_BYTES = 4096;               // two 128-row blocks
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t SFA_COL = 256, SFB_COL = 288;
+constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
 struct Params {
   const uint8_t* sfa;   // blocked scales of A: ceil(M/128) row blocks x sf_atoms_k atoms of 512 B
@@ -130,7 +132,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 4);
+    mbar_init(tempty_bar, 8);
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -193,13 +195,14 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
           const uint32_t sfa0 = b0 + B_BYTES, sfb0 = sfa0 + SFA_BYTES;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-          // scale tiles -> TMEM: atom a of A to columns SFA_COL + 4a; of B (two 128-row blocks)
-          // to SFB_COL + 8a + 4r.  Source: 32 rows of 16 bytes, 8-row groups 128 bytes apart.
+          // scale tiles -> this stage's TMEM region: atom a of A to columns sfa_col + 4a; of B (two
+          // 128-row blocks) to sfb_col + 8a + 4r.  Source: 32 rows of 16 bytes, 8-row groups 128 B apart.
+          const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
           for (int a = 0; a < atoms; ++a) {
-            sf_copy_to_tmem(tmem_base + SFA_COL + 4 * a, make_smem_desc(sfa0 + a * 512, 0, 128, kSwizzleNone));
+            sf_copy_to_tmem(sfa_col + 4 * a, make_smem_desc(sfa0 + a * 512, 0, 128, kSwizzleNone));
 #pragma unroll
             for (int r = 0; r < 2; ++r)
-              sf_copy_to_tmem(tmem_base + SFB_COL + 8 * a + 4 * r,
+              sf_copy_to_tmem(sfb_col + 8 * a + 4 * r,
                               make_smem_desc(sfb0 + r * (SFB_BYTES / 2) + a * 512, 0, 128, kSwizzleNone));
           }
           const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in this k-block
@@ -209,8 +212,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             const uint64_t bd = make_smem_desc(b0 + ks * 32, 16, 1024, kSwizzle128B);
             const int atom = NV ? ks : (ks >> 1);
             const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
-            umma_fp4<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id), tmem_base + SFA_COL + 4 * atom,
-                         tmem_base + SFB_COL + 8 * atom, (kb > kb0) || (ks != 0));
+            umma_fp4<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id), sfa_col + 4 * atom, sfb_col + 8 * atom,
+                         (kb > kb0) || (ks != 0));
           }
           umma_commit(empty_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
@@ -220,7 +223,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     }
   } else {
     // ------------------------------- epilogue ---------------------------------------------------
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;        // TMEM lanes this warp may read: 32*quarter .. +31
+    const int half = (warp - 2) >> 2;    // which 128 of the tile's 256 columns
     const float alpha = *p.alpha;
     uint32_t it = 0;
     bool ok = true;
@@ -229,50 +233,56 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       work_coords(p, w, mb, nb, sp);
       if (!(ok = mbar_wait(tfull_bar, it & 1, abort_flag))) break;
       tc_fence_after();
-      const int row = mb * BM + quarter * 32 + lane;
-      const int col0 = nb * BN;
-      const bool row_ok = row < p.m;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
-        tmem_ld_wait();
-        const int col = col0 + c * 32;
-        if (!row_ok || col >= p.n) continue;
-        if (p.splits == 1) {
-          __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col;
-          if (col + 32 <= p.n) {
+      // drain this thread's row x 128 columns, then hand the accumulator back to the MMA warp
+      uint32_t r[128];
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint4 o;
-              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * u + 2 * v]) * alpha,
-                                                               __uint_as_float(r[8 * u + 2 * v + 1]) * alpha);
-                ow[v] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(dst + 8 * u) = o;
-            }
-          } else {
-            for (int u = 0; u < 32 && col + u < p.n; ++u) dst[u] = __float2bfloat16_rn(__uint_as_float(r[u]) * alpha);
-          }
-        } else {
-          float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col;
-          if (col + 32 <= p.n) {
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              *reinterpret_cast<float4*>(dst + 4 * u) =
-                  make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]), __uint_as_float(r[4 * u + 2]),
-                              __uint_as_float(r[4 * u + 3]));
-          } else {
-            for (int u = 0; u < 32 && col + u < p.n; ++u) dst[u] = __uint_as_float(r[u]);
-          }
-        }
+      for (int c = 0; c < 4; ++c) {
+        uint32_t (&rc)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[c * 32]);
+        tmem_ld_32x32(taddr + c * 32, rc);
       }
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar);
+
+      const int row = mb * BM + quarter * 32 + lane;
+      const int col0 = nb * BN + half * 128;
+      if (row >= p.m) continue;
+      if (p.splits == 1) {
+        __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col0;
+        if (col0 + 128 <= p.n) {
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * u + 2 * v]) * alpha,
+                                                             __uint_as_float(r[8 * u + 2 * v + 1]) * alpha);
+              ow[v] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * u) = o;
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 128; ++u)
+            if (col0 + u < p.n) dst[u] = __float2bfloat16_rn(__uint_as_float(r[u]) * alpha);
+        }
+      } else {
+        float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col0;
+        if (col0 + 128 <= p.n) {
+#pragma unroll
+          for (int u = 0; u < 32; ++u)
+            *reinterpret_cast<float4*>(dst + 4 * u) =
+                make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]), __uint_as_float(r[4 * u + 2]),
+                            __uint_as_float(r[4 * u + 3]));
+        } else {
+#pragma unroll
+          for (int u = 0; u < 128; ++u)
+            if (col0 + u < p.n) dst[u] = __uint_as_float(r[u]);
+        }
+      }
     }
   }
 

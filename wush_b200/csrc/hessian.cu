@@ -53,6 +53,7 @@ struct Params {
   int tokens;
   int n_tiles;
   int first_block;  // first 128-row block of this launch (row panels can be launched separately)
+  int ksplit;       // CTAs sharing the token range of one tile (> 1: results are added with atomics)
   int lower_only;   // do not mirror into the upper triangle
   int* status;      // optional device word, set to 1 when a bounded wait ran out
 };
@@ -68,6 +69,16 @@ __device__ __forceinline__ void tile_coords(int t, int first_block, int& bi, int
   }
   bi = b;
   bj = t;
+}
+
+// work item w -> tile and the k-block range [kb0, kb1) of its token split.  Tile is the fast index:
+// CTAs running at the same time then read the same tokens (different channels), so a block of X
+// is fetched from HBM once and served to all of them from L2.
+__device__ __forceinline__ void work_range(const Params& p, int w, int k_blocks, int& t, int& kb0, int& kb1) {
+  const int sp = w / p.n_tiles;
+  t = w - sp * p.n_tiles;
+  kb0 = (int)((int64_t)sp * k_blocks / p.ksplit);
+  kb1 = (int)((int64_t)(sp + 1) * k_blocks / p.ksplit);
 }
 
 __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
@@ -109,6 +120,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   const int k_blocks = (p.tokens + KT - 1) / KT;
+  const int n_work = p.n_tiles * p.ksplit;
 
   if (warp == 0) {
     // ------------------------------- TMA producer ---------------------------------------------
@@ -117,10 +129,11 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       int s = 0;
       uint32_t round = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-        int bi, bj;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        int t, kbeg, kend, bi, bj;
+        work_range(p, w, k_blocks, t, kbeg, kend);
         tile_coords(t, p.first_block, bi, bj);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kbeg; kb < kend; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
@@ -140,13 +153,15 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       int s = 0;
       uint32_t round = 0, it = 0;  // it counts chunks: accumulator buffer = it & 1
       bool ok = true;
-      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-        for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += CHUNK_KB, ++it) {
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        int t, kbeg, kend;
+        work_range(p, w, k_blocks, t, kbeg, kend);
+        for (int kb0 = kbeg; kb0 < kend && ok; kb0 += CHUNK_KB, ++it) {
           const uint32_t buf = it & 1, use = it >> 1;
           if (!(ok = mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag))) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int kb1 = min(kb0 + CHUNK_KB, k_blocks);
+          const int kb1 = min(kb0 + CHUNK_KB, kend);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
             tc_fence_after();
@@ -172,13 +187,14 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
     const int half = (warp - 2) >> 2;    // which 128 of the tile's 256 columns
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-      int bi, bj;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      int t, kbeg, kend, bi, bj;
+      work_range(p, w, k_blocks, t, kbeg, kend);
       tile_coords(t, p.first_block, bi, bj);
       float acc[128];
 #pragma unroll
       for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
-      for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += CHUNK_KB, ++it) {
+      for (int kb0 = kbeg; kb0 < kend && ok; kb0 += CHUNK_KB, ++it) {
         const uint32_t buf = it & 1, use = it >> 1;
         if (!(ok = mbar_wait(tfull_bar(buf), use & 1, abort_flag))) break;
         tc_fence_after();
@@ -206,6 +222,21 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       for (int c = 0; c < 4; ++c) {
         const int jc = jh + c * 32;
         if (jc > bi * BM + BM - 1) continue;  // chunk above the diagonal for every row of the tile
+        if (p.ksplit > 1) {
+          // several CTAs add into the same tile: fire-and-forget vector reductions (lower-only mode)
+          if (row_ok && jc + 31 <= i) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              atomicAdd(reinterpret_cast<float4*>(hrow + jc + 4 * u),
+                        make_float4(acc[c * 32 + 4 * u], acc[c * 32 + 4 * u + 1], acc[c * 32 + 4 * u + 2],
+                                    acc[c * 32 + 4 * u + 3]));
+          } else {
+#pragma unroll
+            for (int u = 0; u < 32; ++u)
+              if (row_ok && jc + u <= i) atomicAdd(hrow + jc + u, acc[c * 32 + u]);
+          }
+          continue;
+        }
         if (row_ok && jc + 31 <= i) {
           // chunk entirely in the lower triangle of this row (and inside the matrix)
 #pragma unroll
@@ -275,7 +306,20 @@ static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidde
   int64_t n_tiles = 0;
   for (int b = b0; b < b1; ++b) n_tiles += (b >> 1) + 1;
   // column blocks past the matrix edge never exist: bj <= bi/2 implies bj*256 <= bi*128 < hidden
-  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+  // Token splits: only in lower-only mode (the mirror needs final values).  Pick the split count that
+  // wastes the least of the last wave, keeping at least 1024 tokens per split.
+  const int sms = sm_count();
+  int ksplit = 1;
+  if (flags & WUSH_HESSIAN_LOWER_ONLY) {
+    const int max_split = (int)(tokens / 1024 < 1 ? 1 : (tokens / 1024 > 16 ? 16 : tokens / 1024));
+    double best = 1e30;
+    for (int ks = 1; ks <= max_split; ++ks) {
+      const double work = (double)n_tiles * ks, waves = (double)((int64_t)(work + sms - 1) / sms);
+      const double cost = waves * sms / work + 0.02 * ks;   // relative time, penalty per extra pass of atomics over H
+      if (cost < best - 1e-9) { best = cost; ksplit = ks; }
+    }
+  }
+  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
 
   static bool attr_set = false;
   if (!attr_set) {
@@ -284,33 +328,45 @@ static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidde
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  int grid = sm_count();
-  if (grid > n_tiles) grid = (int)n_tiles;
+  int grid = sms;
+  if (grid > n_tiles * ksplit) grid = (int)(n_tiles * ksplit);
   hess::hessian_kernel<<<grid, hess::THREADS, hess::SMEM_BYTES, stream>>>(map, p);
   return (int)cudaGetLastError();
 }
 
 namespace wush {
 namespace hess {
-// Lower triangle (already summed) -> scaled lower triangle and its mirror image.  One thread per
-// 4 consecutive columns of a row; the mirrored writes are strided, the volume is 2 passes over H.
-__global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale) {
-  const int64_t quads = hidden / 4;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < hidden * quads;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t i = idx / quads, j0 = (idx % quads) * 4;
-    if (j0 > i) continue;
-    float4 v = *reinterpret_cast<float4*>(h + i * hidden + j0);
-    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-    const float e[4] = {v.x, v.y, v.z, v.w};
-    if (j0 + 3 <= i) {
-      *reinterpret_cast<float4*>(h + i * hidden + j0) = v;
-    } else {
-      for (int u = 0; u < 4; ++u)
-        if (j0 + u <= i) h[i * hidden + j0 + u] = e[u];
+// Lower triangle (already summed) -> scaled lower triangle and its mirror image, 32 x 32 tiles:
+// a block reads tile (bi, bj), bj <= bi, scales it in place and writes its transpose to (bj, bi)
+// through shared memory, so both the reads and the mirrored writes are coalesced.
+__global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale, int64_t tiles_per_side) {
+  __shared__ float tile[32][33];
+  const int64_t n_tiles = tiles_per_side * (tiles_per_side + 1) / 2;
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    // t -> (bi, bj) with bj <= bi
+    int64_t bi = (int64_t)((sqrt(8.0 * (double)t + 1.0) - 1.0) * 0.5);
+    while (bi * (bi + 1) / 2 > t) --bi;
+    while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
+    const int64_t bj = t - bi * (bi + 1) / 2;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 256 threads: 8 rows per pass
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t i = bi * 32 + r, j = bj * 32 + tx;
+      float v = 0.0f;
+      if (i < hidden && j < hidden && j <= i) {
+        v = h[i * hidden + j] * scale;
+        h[i * hidden + j] = v;
+      }
+      tile[r][tx] = v;
     }
-    for (int u = 0; u < 4; ++u)
-      if (j0 + u < i) h[(j0 + u) * hidden + i] = e[u];
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      // element (j_row, i_col) of the mirrored tile = tile[tx][r]
+      const int64_t jr = bj * 32 + r, ic = bi * 32 + tx;
+      if (jr < hidden && ic < hidden && jr < ic) h[jr * hidden + ic] = tile[tx][r];
+    }
+    __syncthreads();
   }
 }
 }  // namespace hess
@@ -330,10 +386,10 @@ extern "C" int wush_hessian_finalize(float* h, int64_t hidden, float scale, void
   if (!h) return WUSH_ERR_NULL_POINTER;
   if (hidden <= 0 || hidden % 4 != 0) return WUSH_ERR_BAD_SHAPE;
   if ((uintptr_t)h & 15) return WUSH_ERR_BAD_ALIGNMENT;
-  const int64_t work = hidden * (hidden / 4);
-  int64_t blocks = (work + 255) / 256;
+  const int64_t side = (hidden + 31) / 32;
+  int64_t blocks = side * (side + 1) / 2;
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  hess::finalize_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, scale);
+  hess::finalize_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, scale, side);
   return (int)cudaGetLastError();
 }

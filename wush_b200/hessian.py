@@ -87,7 +87,7 @@ class DistributedHessian:
     (gloo) with a stand-in for the CUDA kernels; the defaults call the kernels and need a GPU.
     """
 
-    def __init__(self, hidden: int, device, group=None, panels: int = 8, accumulate_fn=None, finalize_fn=None):
+    def __init__(self, hidden: int, device, group=None, panels: int = 4, accumulate_fn=None, finalize_fn=None):
         import torch.distributed as dist
         self.hidden, self.device, self.group, self.panels = hidden, torch.device(device), group, panels
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
@@ -113,10 +113,13 @@ class DistributedHessian:
         x = x.reshape(-1, x.shape[-1])
         assert not self._reduced
         cuda = self._comm_stream is not None
+        if self.world == 1:
+            self._accumulate(self.raw, x, 0, self.hidden, True)
+            self.local_tokens += x.shape[0]
+            self._reduced = True
+            return
         for (r0, r1) in panel_bounds(self.hidden, self.panels):
             self._accumulate(self.raw, x, r0, r1, True)
-            if self.world == 1:
-                continue
             if cuda:
                 done = torch.cuda.Event()
                 done.record()
