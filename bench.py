@@ -158,7 +158,8 @@ def workload_config(n_gpus: int) -> dict:
     return {"workload": f"fused WUSH transform + MXFP4 quantize, {TOKENS} tokens x {HIDDEN} channels bf16 per GPU, "
                         f"per-group 32x32 matrices, N(0,1) + 0.5% outlier channels x50 (seeded)",
             "tokens_per_gpu": TOKENS, "hidden": HIDDEN, "group": GROUP, "format": "mxfp4",
-            "l2_policy": "inputs (470 MB) and outputs (125 MB) larger than the 126 MB L2, no flush needed",
+            "l2_policy": f"inputs ({TOKENS * HIDDEN * 2 / 1e6:.0f} MB) and outputs ({TOKENS * HIDDEN * 0.53125 / 1e6:.0f} MB) "
+                         "against a 126 MB L2: larger than L2 at the default size, so no flush between iterations",
             "parallelism": f"rows sharded over {n_gpus} GPU(s), no collective",
             "baseline_metric": "MXFP4 W4A4 GEMM TFLOPS + fused transform-quant GB/s; Hessian tok/s @1/2/4/8"}
 
@@ -295,6 +296,18 @@ def run_ours(args) -> None:
     peaks, peak_kind = measured_peaks()
     warmup = max(args.warmup, 3)
 
+    if args.only in ("gemm", "hessian"):
+        if args.only == "gemm":
+            res = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
+        else:
+            res = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=args.hess_hidden)
+        if rank == 0:
+            res.update({"n_gpus": world, "only": args.only, "data": "synthetic"})
+            print(json.dumps(res), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- fused transform + quantize: every rank its own shard of rows, same matrices -------------
     x_host = synth.activations(TOKENS, HIDDEN, seed=100 + rank).pin_memory()
     mat = synth.to_bf16_tensor(synth.wush_matrix(HIDDEN, GROUP)).to(dev)
@@ -360,7 +373,7 @@ def run_ours(args) -> None:
     del x, q, sf, x_host, q_host, sf_host
 
     extra = {}
-    if not args.kernel_only:
+    if not args.kernel_only and args.only == "all":
         gemm = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
         hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
         hess_ffn = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
@@ -371,7 +384,7 @@ def run_ours(args) -> None:
         e2e_value = world * alg * args.steps / (e2e_ms * 1e-3) / 1e9
         achieved = alg / (kernel_ms * 1e-3) / 1e9
         cpu = None
-        if world == 1 and not args.kernel_only:
+        if world == 1 and not args.kernel_only and args.only == "all":
             cpu = cpu_quant_throughput(512, HIDDEN, repeats=2)
             cpu.pop("seconds", None)
             extra["gemm"]["cpu_baseline"] = cpu_gemm_throughput()
@@ -453,8 +466,16 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
+    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian"],
+                    help="run one section only (profiler captures of a single kernel on a small case)")
+    ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
+    ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)
+    ap.add_argument("--hess-hidden", type=int, default=HESS_HIDDEN)
     args = ap.parse_args()
-    globals()["TOKENS"], globals()["HIDDEN"] = args.tokens, args.hidden
+    g = globals()
+    g["TOKENS"], g["HIDDEN"] = args.tokens, args.hidden
+    g["GEMM_M"] = g["GEMM_N"] = g["GEMM_K"] = args.gemm_size
+    g["HESS_TOKENS"] = args.hess_tokens
     if args.impl == "reference":
         run_reference(args)
     else:

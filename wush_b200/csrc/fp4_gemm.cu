@@ -4,17 +4,21 @@
 // the per-group scales arrive in the 128x4 blocked layout: E8M0 per 32 elements (MXFP4) or
 // E4M3 per 16 elements (NVFP4).  The products run on tcgen05.mma kind::mxf4 /
 // kind::mxf4nvf4 with block scaling: 128 x 256 output tile per CTA, K = 64 per instruction,
-// fp32 accumulation in TMEM, scale factors copied shared memory -> TMEM with tcgen05.cp.
+// fp32 accumulation in TMEM, scale factors written to TMEM from registers with tcgen05.st
+// (tcgen05.cp copies issued between the MMAs were measured to cost a quarter of the run time:
+// they execute in the MMA pipe; stores from ordinary warps do not).
 //
 // Persistent CTAs, one per SM:
 //   warp 0      producer: per 256-element k-block one TMA box each for A (128 rows x 128 B) and
-//               B (256 rows x 128 B), 128-byte swizzle, plus bulk copies of the scale tiles
-//   warp 1      allocates TMEM; per k-block copies the scale tiles to TMEM and issues 4 MMAs
-//   warps 2..9  epilogue: each thread drains one row x 128 columns of the accumulator into registers,
-//               releases TMEM (the next tile's MMAs start), then * alpha -> bf16 -> global (or fp32
-//               partials when the K range is split across CTAs; a second kernel then reduces them)
+//               B (256 rows x 128 B), 128-byte swizzle
+//   warp 1      allocates TMEM; per k-block issues 4 MMAs
+//   warps 10..13 scale feeders, one per TMEM lane quarter: global -> registers -> TMEM, stages ahead
+//   warps 2..9  epilogue: each thread drains one row x 128 columns of the accumulator, scaling and
+//               packing to bf16 as it goes (64 registers), releases TMEM (the next tile's MMAs
+//               start) and only then stores.  When the K range is split across CTAs it writes fp32
+//               partial tiles instead and a second kernel reduces them
 // TMEM columns: [0,256) accumulator; from 256 on, one 48-column scale region per pipeline stage
-// (16 for A, 32 for B), so a stage's scale copy never waits for the previous stage's MMAs.
+// (16 for A, 32 for B), so the feeders can run ahead of the MMAs.
 // All mbarrier waits are bounded (see sm100.cuh).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -33,11 +37,10 @@ constexpr int BM = 128, BN = 256, BK = 256;   // BK in elements = 128 bytes per 
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK / 2;          // 16 KB
 constexpr int B_BYTES = BN * BK / 2;          // 32 KB
-constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4); MXFP4 uses 2
-constexpr int SFB_BYTES = 4096;               // two 128-row blocks
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int THREADS = 320;
+constexpr int THREADS = 448;                  // 14 warps: producer, MMA, 8 epilogue, 4 scale feeders
+constexpr int EPI_WARP0 = 2, SF_WARP0 = 10;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
@@ -55,17 +58,13 @@ struct Params {
   int* status;
 };
 
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
-      : "memory");
+// registers -> TMEM: 32 lanes (this warp's quarter) x N consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint4& a, const uint4& b) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+               ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
 }
-
-// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into all four lane quarters
-__device__ __forceinline__ void sf_copy_to_tmem(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(taddr), "l"(sdesc) : "memory");
-}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 template <bool NV>
 __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -115,8 +114,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  // bars[0..S): full, [S..2S): empty, [2S]: tmem_full, [2S+1]: tmem_empty
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+  // bars[0..S): full, [S..2S): empty, [2S]: tmem_full, [2S+1]: tmem_empty, [2S+2..3S+2): scales in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,11 +124,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   auto full_bar = [&](int s) { return bar_base + 8 * s; };
   auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
   const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES), tempty_bar = bar_base + 8 * (2 * STAGES + 1);
+  auto sf_bar = [&](int s) { return bar_base + 8 * (2 * STAGES + 2 + s); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(sf_bar(s), 4);   // one arrival per feeder warp
     }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, 8);
@@ -160,19 +161,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         split_range(p, sp, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
-          // scale atoms really present in this k-block (the last block may hold fewer)
-          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-          const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
-          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES + sf_bytes * (1 + b_blocks));
+          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
           tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
           tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
-          bulk_load(dst + A_BYTES + B_BYTES, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
-                    full_bar(s));
-          for (int r = 0; r < b_blocks; ++r)
-            bulk_load(dst + A_BYTES + B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
-                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, full_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -193,18 +185,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
           tc_fence_after();
           const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
-          const uint32_t sfa0 = b0 + B_BYTES, sfb0 = sfa0 + SFA_BYTES;
+          if (!(ok = mbar_wait(sf_bar(s), round & 1, abort_flag))) break;   // this stage's scales are in TMEM
+          tc_fence_after();
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-          // scale tiles -> this stage's TMEM region: atom a of A to columns sfa_col + 4a; of B (two
-          // 128-row blocks) to sfb_col + 8a + 4r.  Source: 32 rows of 16 bytes, 8-row groups 128 B apart.
+          // atom a of A sits in columns sfa_col + 4a, of B (two 128-row blocks) in sfb_col + 8a + 4r
           const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
-          for (int a = 0; a < atoms; ++a) {
-            sf_copy_to_tmem(sfa_col + 4 * a, make_smem_desc(sfa0 + a * 512, 0, 128, kSwizzleNone));
-#pragma unroll
-            for (int r = 0; r < 2; ++r)
-              sf_copy_to_tmem(sfb_col + 8 * a + 4 * r,
-                              make_smem_desc(sfb0 + r * (SFB_BYTES / 2) + a * 512, 0, 128, kSwizzleNone));
-          }
           const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in this k-block
           for (int ks = 0; ks < ksteps; ++ks) {
             // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; 64 elements = 32 bytes
@@ -221,10 +206,52 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (ok) umma_commit(tfull_bar);
       }
     }
-  } else {
+  } else if (warp >= SF_WARP0) {
+    // ------------------------------- scale feeders ------------------------------------------------
+    // Lane l of every feeder holds row l of each 128 x 4 scale atom (16 bytes = 4 columns: one per
+    // 32-row group, 4 consecutive k-scales per column) and stores it to its own TMEM lane quarter.
+    const int quarter = warp & 3;
+    int s = 0;
+    uint32_t round = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      int mb, nb, sp, kb0, kb1;
+      work_coords(p, w, mb, nb, sp);
+      split_range(p, sp, kb0, kb1);
+      const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+        // issue the loads before waiting for the TMEM region to be free
+        uint4 va[ATOMS], vb[ATOMS][2];
+        const uint8_t* ga = p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512 + lane * 16;
+        const uint8_t* gb = p.sfb + ((int64_t)(nb * 2) * p.sf_atoms_k + kb * ATOMS) * 512 + lane * 16;
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+          va[a] = vb[a][0] = vb[a][1] = make_uint4(0, 0, 0, 0);
+          if (a < atoms) {
+            va[a] = ld_nc_v4(ga + a * 512);
+            vb[a][0] = ld_nc_v4(gb + a * 512);
+            if (b_blocks > 1) vb[a][1] = ld_nc_v4(gb + (int64_t)p.sf_atoms_k * 512 + a * 512);
+          }
+        }
+        if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t sfa_col = tmem_base + ((uint32_t)(quarter * 32) << 16) + SF_COL0 + s * SF_STAGE_COLS;
+#pragma unroll
+        for (int a = 0; a < ATOMS; a += 2) tmem_st_x8(sfa_col + 4 * a, va[a], va[a + 1]);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sf_bar(s));
+        if (++s == STAGES) { s = 0; ++round; }
+      }
+    }
+  } else if (warp >= EPI_WARP0) {
     // ------------------------------- epilogue ---------------------------------------------------
     const int quarter = warp & 3;        // TMEM lanes this warp may read: 32*quarter .. +31
-    const int half = (warp - 2) >> 2;    // which 128 of the tile's 256 columns
+    const int half = (warp - EPI_WARP0) >> 2;    // which 128 of the tile's 256 columns
     const float alpha = *p.alpha;
     uint32_t it = 0;
     bool ok = true;
@@ -233,55 +260,59 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       work_coords(p, w, mb, nb, sp);
       if (!(ok = mbar_wait(tfull_bar, it & 1, abort_flag))) break;
       tc_fence_after();
-      // drain this thread's row x 128 columns, then hand the accumulator back to the MMA warp
-      uint32_t r[128];
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t (&rc)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[c * 32]);
-        tmem_ld_32x32(taddr + c * 32, rc);
-      }
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar);
-
       const int row = mb * BM + quarter * 32 + lane;
       const int col0 = nb * BN + half * 128;
-      if (row >= p.m) continue;
       if (p.splits == 1) {
+        // drain this thread's row x 128 columns as packed bf16, then hand the accumulator back
+        uint32_t packed[64];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            const __nv_bfloat162 h =
+                __floats2bfloat162_rn(__uint_as_float(r[2 * v]) * alpha, __uint_as_float(r[2 * v + 1]) * alpha);
+            packed[c * 16 + v] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar);
+        if (row >= p.m) continue;
         __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col0;
         if (col0 + 128 <= p.n) {
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * u + 2 * v]) * alpha,
-                                                             __uint_as_float(r[8 * u + 2 * v + 1]) * alpha);
-              ow[v] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(dst + 8 * u) = o;
-          }
+          for (int u = 0; u < 16; ++u)
+            *reinterpret_cast<uint4*>(dst + 8 * u) =
+                make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
         } else {
 #pragma unroll
-          for (int u = 0; u < 128; ++u)
-            if (col0 + u < p.n) dst[u] = __float2bfloat16_rn(__uint_as_float(r[u]) * alpha);
+          for (int u = 0; u < 64; ++u)       // n % 8 == 0: pairs never straddle the edge
+            if (col0 + 2 * u < p.n) *reinterpret_cast<uint32_t*>(dst + 2 * u) = packed[u];
         }
       } else {
+        // split K: fp32 partial tile, stored chunk by chunk before the accumulator is released
         float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col0;
-        if (col0 + 128 <= p.n) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.m) {
 #pragma unroll
-          for (int u = 0; u < 32; ++u)
-            *reinterpret_cast<float4*>(dst + 4 * u) =
-                make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]), __uint_as_float(r[4 * u + 2]),
-                            __uint_as_float(r[4 * u + 3]));
-        } else {
-#pragma unroll
-          for (int u = 0; u < 128; ++u)
-            if (col0 + u < p.n) dst[u] = __uint_as_float(r[u]);
+            for (int u = 0; u < 8; ++u)     // n % 8 == 0: groups of 4 never straddle the edge
+              if (col0 + c * 32 + 4 * u < p.n)
+                *reinterpret_cast<float4*>(dst + c * 32 + 4 * u) =
+                    make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]),
+                                __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+          }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar);
       }
     }
   }

@@ -52,23 +52,34 @@ struct Params {
   int hidden;
   int tokens;
   int n_tiles;
-  int first_block;  // first 128-row block of this launch (row panels can be launched separately)
+  int first_block;  // 128-row blocks [first_block, last_block) of this launch (row panels can be launched separately)
+  int last_block;
   int ksplit;       // CTAs sharing the token range of one tile (> 1: results are added with atomics)
   int lower_only;   // do not mirror into the upper triangle
   int* status;      // optional device word, set to 1 when a bounded wait ran out
 };
 
-// tile t -> (row block bi of 128, column block bj of 256); row block bi has bi/2 + 1 column blocks
-__device__ __forceinline__ void tile_coords(int t, int first_block, int& bi, int& bj) {
-  int b = first_block;
-  while (true) {
-    const int n = (b >> 1) + 1;
-    if (t < n) break;
-    t -= n;
-    ++b;
+// tile t -> (row block bi of 128, column block bj of 256); row block bi has bi/2 + 1 column blocks.
+// Tiles are ordered in bands of 16 row blocks, column block by column block inside a band, so the
+// ~148 tiles in flight cover a compact rectangle of H and share their X columns through L2.
+constexpr int BAND = 16;
+__device__ __forceinline__ void tile_coords(int t, int first_block, int last_block, int& bi, int& bj) {
+  for (int lo = first_block;; lo += BAND) {
+    const int hi = min(lo + BAND, last_block);          // row blocks [lo, hi)
+    for (int c = 0; c <= (hi - 1) >> 1; ++c) {          // column blocks that some row of the band reaches
+      const int first = max(lo, 2 * c);                 // rows bi >= 2c own column block c
+      const int cnt = hi - first;
+      if (t < cnt) {
+        bi = first + t;
+        bj = c;
+        return;
+      }
+      t -= cnt;
+    }
+    if (hi >= last_block) break;
   }
-  bi = b;
-  bj = t;
+  bi = first_block;   // not reached for t < n_tiles
+  bj = 0;
 }
 
 // work item w -> tile and the k-block range [kb0, kb1) of its token split.  Tile is the fast index:
@@ -132,7 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         int t, kbeg, kend, bi, bj;
         work_range(p, w, k_blocks, t, kbeg, kend);
-        tile_coords(t, p.first_block, bi, bj);
+        tile_coords(t, p.first_block, p.last_block, bi, bj);
         for (int kb = kbeg; kb < kend; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
@@ -190,7 +201,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
       int t, kbeg, kend, bi, bj;
       work_range(p, w, k_blocks, t, kbeg, kend);
-      tile_coords(t, p.first_block, bi, bj);
+      tile_coords(t, p.first_block, p.last_block, bi, bj);
       float acc[128];
 #pragma unroll
       for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
@@ -319,7 +330,7 @@ static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidde
       if (cost < best - 1e-9) { best = cost; ksplit = ks; }
     }
   }
-  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, b1, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
 
   static bool attr_set = false;
   if (!attr_set) {
