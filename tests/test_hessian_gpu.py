@@ -15,7 +15,8 @@ def _rel(got: np.ndarray, want: np.ndarray):
     return np.abs(got - want).max() / np.abs(want).max(), np.linalg.norm(got - want) / np.linalg.norm(want)
 
 
-@pytest.mark.parametrize("tokens,hidden", [(64, 128), (100, 256), (1, 64), (333, 1000), (2048, 512), (4096, 1024), (16384, 256)])
+@pytest.mark.parametrize("tokens,hidden", [(64, 128), (100, 256), (1, 64), (333, 1000), (2048, 512), (4096, 1024), (16384, 256),
+                                           (70000, 256)])
 def test_hessian_matches_float64(tokens, hidden):
     from wush_b200.hessian import accumulate_hessian
     dev = torch.device("cuda:0")

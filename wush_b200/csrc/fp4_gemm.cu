@@ -4,15 +4,17 @@
 // the per-group scales arrive in the 128x4 blocked layout: E8M0 per 32 elements (MXFP4) or
 // E4M3 per 16 elements (NVFP4).  The products run on tcgen05.mma kind::mxf4 /
 // kind::mxf4nvf4 with block scaling: 128 x 256 output tile per CTA, K = 64 per instruction,
-// fp32 accumulation in TMEM, scale factors written to TMEM from registers with tcgen05.st
-// (tcgen05.cp copies issued between the MMAs were measured to cost a quarter of the run time:
-// they execute in the MMA pipe; stores from ordinary warps do not).
+// fp32 accumulation in TMEM.  Scale tiles travel global -> shared memory with the operands (bulk
+// copies on the same mbarrier) and shared memory -> registers -> TMEM through four feeder warps
+// (tcgen05.st).  tcgen05.cp copies issued between the MMAs were measured to cost a quarter of the
+// run time -- they execute in the MMA pipe -- and feeding from global memory directly made the
+// feeders latency-bound.
 //
 // Persistent CTAs, one per SM:
 //   warp 0      producer: per 256-element k-block one TMA box each for A (128 rows x 128 B) and
-//               B (256 rows x 128 B), 128-byte swizzle
+//               B (256 rows x 128 B), 128-byte swizzle, plus bulk copies of the scale tiles
 //   warp 1      allocates TMEM; per k-block issues 4 MMAs
-//   warps 10..13 scale feeders, one per TMEM lane quarter: global -> registers -> TMEM, stages ahead
+//   warps 10..13 scale feeders, one per TMEM lane quarter: shared memory -> registers -> TMEM
 //   warps 2..9  epilogue: each thread drains one row x 128 columns of the accumulator, scaling and
 //               packing to bf16 as it goes (64 registers), releases TMEM (the next tile's MMAs
 //               start) and only then stores.  When the K range is split across CTAs it writes fp32
@@ -37,7 +39,9 @@ constexpr int BM = 128, BN = 256, BK = 256;   // BK in elements = 128 bytes per 
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK / 2;          // 16 KB
 constexpr int B_BYTES = BN * BK / 2;          // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4); MXFP4 uses 2
+constexpr int SFB_BYTES = 4096;               // two 128-row blocks
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int THREADS = 448;                  // 14 warps: producer, MMA, 8 epilogue, 4 scale feeders
 constexpr int EPI_WARP0 = 2, SF_WARP0 = 10;
@@ -57,6 +61,13 @@ struct Params {
   int sfb_row_blocks;   // 128-row blocks present in sfb
   int* status;
 };
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+      : "memory");
+}
 
 // registers -> TMEM: 32 lanes (this warp's quarter) x N consecutive 32-bit columns
 __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint4& a, const uint4& b) {
@@ -161,10 +172,19 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         split_range(p, sp, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
-          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES);
+          // scale atoms really present in this k-block (the last block may hold fewer)
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
+          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES + sf_bytes * (1 + b_blocks));
           const uint32_t dst = smem_base + s * STAGE_BYTES;
           tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
           tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
+          bulk_load(dst + A_BYTES + B_BYTES, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
+                    full_bar(s));
+          for (int r = 0; r < b_blocks; ++r)
+            bulk_load(dst + A_BYTES + B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
+                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, full_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -208,8 +228,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     }
   } else if (warp >= SF_WARP0) {
     // ------------------------------- scale feeders ------------------------------------------------
-    // Lane l of every feeder holds row l of each 128 x 4 scale atom (16 bytes = 4 columns: one per
-    // 32-row group, 4 consecutive k-scales per column) and stores it to its own TMEM lane quarter.
+    // Lane l of every feeder reads row l of each 128 x 4 scale atom from shared memory (16 bytes =
+    // 4 columns: one per 32-row group, 4 consecutive k-scales per column) and stores it to its own
+    // TMEM lane quarter.  A full stage implies that its TMEM scale region is free: the producer only
+    // refills a stage after the MMAs that read it (and its scales) have completed.
     const int quarter = warp & 3;
     int s = 0;
     uint32_t round = 0;
@@ -218,24 +240,17 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int mb, nb, sp, kb0, kb1;
       work_coords(p, w, mb, nb, sp);
       split_range(p, sp, kb0, kb1);
-      const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
       for (int kb = kb0; kb < kb1; ++kb) {
-        const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-        // issue the loads before waiting for the TMEM region to be free
+        if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+        const uint8_t* sfa = smem + s * STAGE_BYTES + A_BYTES + B_BYTES + lane * 16;
+        const uint8_t* sfb = sfa + SFA_BYTES;
         uint4 va[ATOMS], vb[ATOMS][2];
-        const uint8_t* ga = p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512 + lane * 16;
-        const uint8_t* gb = p.sfb + ((int64_t)(nb * 2) * p.sf_atoms_k + kb * ATOMS) * 512 + lane * 16;
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a) {
-          va[a] = vb[a][0] = vb[a][1] = make_uint4(0, 0, 0, 0);
-          if (a < atoms) {
-            va[a] = ld_nc_v4(ga + a * 512);
-            vb[a][0] = ld_nc_v4(gb + a * 512);
-            if (b_blocks > 1) vb[a][1] = ld_nc_v4(gb + (int64_t)p.sf_atoms_k * 512 + a * 512);
-          }
+          va[a] = *reinterpret_cast<const uint4*>(sfa + a * 512);
+          vb[a][0] = *reinterpret_cast<const uint4*>(sfb + a * 512);
+          vb[a][1] = *reinterpret_cast<const uint4*>(sfb + SFB_BYTES / 2 + a * 512);
         }
-        if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
-        tc_fence_after();
         const uint32_t sfa_col = tmem_base + ((uint32_t)(quarter * 32) << 16) + SF_COL0 + s * SF_STAGE_COLS;
 #pragma unroll
         for (int a = 0; a < ATOMS; a += 2) tmem_st_x8(sfa_col + 4 * a, va[a], va[a + 1]);

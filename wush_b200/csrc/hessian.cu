@@ -297,8 +297,35 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
 
 using namespace wush;
 
+static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
+                              int64_t row_end, int flags, int* status, cudaStream_t stream);
+
+// Tokens per kernel launch.  The CTAs of a launch walk the token axis side by side and share the X
+// blocks they read through L2; over very long token ranges they drift apart and that sharing is lost
+// (measured at hidden 14336: 1230 TFLOP/s with 32768 tokens per launch, 800 with 262144), so long
+// inputs are cut into segments.  Earlier segments only update the lower triangle; the mirror image is
+// written once, by the last segment.
+constexpr int64_t kSegmentTokens = 32768;
+
 static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin, int64_t row_end,
                           int flags, int* status, cudaStream_t stream) {
+  if (tokens <= kSegmentTokens + kSegmentTokens / 2)
+    return hessian_launch_one(h, x, tokens, hidden, row_begin, row_end, flags, status, stream);
+  if (!x || hidden <= 0) return hessian_launch_one(h, x, tokens, hidden, row_begin, row_end, flags, status, stream);
+  const char* xb = static_cast<const char*>(x);
+  for (int64_t t0 = 0; t0 < tokens; t0 += kSegmentTokens) {
+    const int64_t n = tokens - t0 < kSegmentTokens + kSegmentTokens / 2 ? tokens - t0 : kSegmentTokens;
+    const bool last = t0 + n >= tokens;
+    const int rc = hessian_launch_one(h, xb + t0 * hidden * 2, n, hidden, row_begin, row_end,
+                                      last ? flags : (flags | WUSH_HESSIAN_LOWER_ONLY), status, stream);
+    if (rc != 0) return rc;
+    if (last) break;
+  }
+  return 0;
+}
+
+static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
+                              int64_t row_end, int flags, int* status, cudaStream_t stream) {
   if (!h || !x) return WUSH_ERR_NULL_POINTER;
   if (tokens < 0 || hidden <= 0 || hidden % 8 != 0 || tokens > 0x7fffffff || hidden > (1 << 20)) return WUSH_ERR_BAD_SHAPE;
   if (row_begin < 0 || row_end > hidden || row_begin > row_end || row_begin % hess::BM != 0 ||
