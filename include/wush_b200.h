@@ -33,7 +33,8 @@ extern "C" {
 #define WUSH_ERR_BAD_FLAG (-4)
 #define WUSH_ERR_WORKSPACE_TOO_SMALL (-5)
 #define WUSH_ERR_NOT_SM100 (-6)
-#define WUSH_ERR_DEVICE_TIMEOUT (-7) /* a bounded wait inside a kernel ran out; see wush_read_status */
+#define WUSH_ERR_DEVICE_TIMEOUT (-7) /* a bounded wait inside a kernel ran out (reported through `status`) */
+#define WUSH_ERR_TOO_LARGE (-8)      /* problem exceeds a fixed capacity of the entry point */
 
 /* Layout of the per-group scale bytes written by the fused quantize kernels. */
 #define WUSH_SF_ROW_MAJOR 0 /* sf[row * sf_cols + group], sf_cols = ceil(C/G/4)*4 */
@@ -171,6 +172,30 @@ WUSH_API int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const ui
 WUSH_API int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                     const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
                                     size_t workspace_bytes, int splits, int* status, void* stream);
+/*
+ * Split-K MXFP4 GEMM for callers that must not allocate device memory.  (No counterpart in the reference.)
+ *
+ * Some hosts of this library cannot call cudaMalloc on the path where the GEMM runs: a serving loop whose
+ * memory is fully carved up at start-up, a plugin running inside another framework's stream-ordered pool, code
+ * replayed from a captured graph.  For small-M (decode) shapes the GEMM wants scratch for its split-K partial
+ * tiles; this entry point keeps that scratch in a fixed array inside the library (WUSH_GEMM_STATIC_SCRATCH_BYTES
+ * of device memory per GPU that loads the library, held until the process exits), so the caller passes inputs
+ * and the output only.  Same arithmetic and argument meaning as wush_gemm_mxf4_bf16_tn with a workspace.
+ *
+ *   splits   0 = choose (at least 2, reduced until the partial tiles fit); >= 2 forces a value
+ * Returns WUSH_ERR_TOO_LARGE when splits * m * n fp32 values do not fit in the array, WUSH_ERR_BAD_FLAG when K is
+ * too short to be split (fewer than 2 blocks of 256) or `splits` is out of range.
+ * Rules: (1) the first call on each device looks up the array's device address (cudaGetSymbolAddress) and caches
+ * it; make that first call outside any stream capture.  (2) Every call on a device uses the same array: calls
+ * that can overlap on the GPU (different streams without ordering) race and corrupt each other; serialize them.
+ * (3) Nothing needs zeroing: each call overwrites every partial value it later reads.  It calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ */
+#define WUSH_GEMM_STATIC_SCRATCH_BYTES (16u << 20)
+WUSH_API int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                            const float* alpha, void* y, int64_t m, int64_t n, int64_t k, int splits,
+                                            int* status, void* stream);
+
 /* Scratch bytes the automatic split-K choice would use for this problem on the current device (0 = none). */
 WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 

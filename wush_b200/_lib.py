@@ -16,7 +16,7 @@ HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "wush_b200.h")
 ERRORS = {
     -1: "null pointer", -2: "bad shape", -3: "bad alignment", -4: "bad flag or layout",
     -5: "workspace too small", -6: "device is not sm_100", -7: "device-side bounded wait timed out",
-    -8: "size beyond the supported maximum",
+    -8: "problem exceeds a fixed capacity of the entry point",
 }
 
 SF_ROW_MAJOR, SF_BLOCKED = 0, 1
@@ -64,6 +64,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
+    lib.wush_gemm_mxf4_bf16_tn_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, vp, vp]
+    lib.wush_gemm_mxf4_bf16_tn_noalloc.restype = ctypes.c_int
     lib.wush_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.wush_gemm_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib

@@ -26,6 +26,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/wush_b200.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -446,6 +448,64 @@ extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const 
                                       size_t workspace_bytes, int splits, int* status, void* stream) {
   return wush::gemm::gemm_launch(true, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
                                  (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-K MXFP4 GEMM whose partial tiles live in a fixed device array instead of a caller-supplied
+// workspace.  See the declaration in wush_b200.h for who needs this and for the rules.
+// ---------------------------------------------------------------------------------------------
+namespace wush {
+namespace gemm {
+
+constexpr size_t kStaticScratchFloats = WUSH_GEMM_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_splitk_scratch[kStaticScratchFloats];
+
+// Device address of g_splitk_scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel could use, so the address is looked up once per
+// device (with that device current) and cached.
+static int static_scratch_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cache[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return WUSH_ERR_BAD_SHAPE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_splitk_scratch);
+    if (e != cudaSuccess) return (int)e;
+    cache[dev] = static_cast<float*>(p);
+  }
+  *out = cache[dev];
+  return WUSH_OK;
+}
+
+}  // namespace gemm
+}  // namespace wush
+
+extern "C" int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                              const float* alpha, void* y, int64_t m, int64_t n, int64_t k, int splits,
+                                              int* status, void* stream) {
+  using namespace wush::gemm;
+  if (m < 0 || n <= 0 || k <= 0) return WUSH_ERR_BAD_SHAPE;
+  if (splits < 0) return WUSH_ERR_BAD_FLAG;
+  const int k_blocks = (int)((k + BK - 1) / BK);
+  if (splits == 0) {
+    const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    splits = choose_splits(tiles, k_blocks, wush::sm_count());
+    // keep the partial tiles inside the fixed array, but stay a split-K launch
+    while (splits > 2 && (size_t)splits * m * n > kStaticScratchFloats) --splits;
+    if (splits < 2) splits = 2;
+  }
+  if (splits < 2 || splits > k_blocks) return WUSH_ERR_BAD_FLAG;   // K too short to split, or a forced value out of range
+  if ((size_t)splits * (size_t)m * (size_t)n > kStaticScratchFloats) return WUSH_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != WUSH_OK) return rc;
+  return gemm_launch(false, a, b, sfa, sfb, alpha, y, m, n, k, scratch, WUSH_GEMM_STATIC_SCRATCH_BYTES, splits, status,
+                     (cudaStream_t)stream);
 }
 
 extern "C" size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
