@@ -68,4 +68,4 @@ def test_panel_bounds_cover_rows():
             b = panel_bounds(hidden, panels)
             assert b[0][0] == 0 and b[-1][1] == hidden
             assert all(b[i][1] == b[i + 1][0] for i in range(len(b) - 1))
-            assert all(r0 % 128 == 0 for r0, _ in b)
+            assert all(r0 % 256 == 0 for r0, _ in b)

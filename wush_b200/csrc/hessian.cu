@@ -92,6 +92,64 @@ __device__ __forceinline__ void work_range(const Params& p, int w, int k_blocks,
   kb1 = (int)((int64_t)(sp + 1) * k_blocks / p.ksplit);
 }
 
+// Add this thread's 128 accumulated values (row i, columns jh .. jh+127) into H.  `tile_last_row` is the
+// last row of the CTA's tile: 32-column chunks that start beyond it lie above the diagonal for every row
+// of the tile and are skipped uniformly.
+__device__ __forceinline__ void update_h(const Params& p, float (&acc)[128], int i, int jh, int tile_last_row) {
+  const bool row_ok = i < p.hidden;
+  float* hrow = p.h + (int64_t)i * p.ldh;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int jc = jh + c * 32;
+    if (jc > tile_last_row) continue;
+    if (p.ksplit > 1) {
+      // several CTAs add into the same tile: fire-and-forget vector reductions (lower-only mode)
+      if (row_ok && jc + 31 <= i) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          atomicAdd(reinterpret_cast<float4*>(hrow + jc + 4 * u),
+                    make_float4(acc[c * 32 + 4 * u], acc[c * 32 + 4 * u + 1], acc[c * 32 + 4 * u + 2],
+                                acc[c * 32 + 4 * u + 3]));
+      } else {
+#pragma unroll
+        for (int u = 0; u < 32; ++u)
+          if (row_ok && jc + u <= i) atomicAdd(hrow + jc + u, acc[c * 32 + u]);
+      }
+      continue;
+    }
+    if (row_ok && jc + 31 <= i) {
+      // chunk entirely in the lower triangle of this row (and inside the matrix)
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float4 o = *reinterpret_cast<const float4*>(hrow + jc + 4 * u);
+        o.x += acc[c * 32 + 4 * u];
+        o.y += acc[c * 32 + 4 * u + 1];
+        o.z += acc[c * 32 + 4 * u + 2];
+        o.w += acc[c * 32 + 4 * u + 3];
+        *reinterpret_cast<float4*>(hrow + jc + 4 * u) = o;
+        acc[c * 32 + 4 * u] = o.x; acc[c * 32 + 4 * u + 1] = o.y;
+        acc[c * 32 + 4 * u + 2] = o.z; acc[c * 32 + 4 * u + 3] = o.w;
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < 32; ++u) {
+        if (row_ok && jc + u <= i) {
+          acc[c * 32 + u] += hrow[jc + u];
+          hrow[jc + u] = acc[c * 32 + u];
+        }
+      }
+    }
+    if (!p.lower_only) {
+      // mirror: element (i, j), j < i, also goes to (j, i); lanes hold consecutive i
+#pragma unroll
+      for (int u = 0; u < 32; ++u) {
+        const int j = jc + u;
+        if (row_ok && j < i) p.h[(int64_t)j * p.ldh + i] = acc[c * 32 + u];
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
   extern __shared__ uint8_t smem_unaligned[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
@@ -224,61 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       }
       if (!ok) break;
 
-      // ---- H update from registers: row i, columns jh .. jh+127 -----------------------------------
-      const int i = bi * BM + quarter * 32 + lane;
-      const int jh = bj * BN + half * 128;
-      const bool row_ok = i < p.hidden;
-      float* hrow = p.h + (int64_t)i * p.ldh;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int jc = jh + c * 32;
-        if (jc > bi * BM + BM - 1) continue;  // chunk above the diagonal for every row of the tile
-        if (p.ksplit > 1) {
-          // several CTAs add into the same tile: fire-and-forget vector reductions (lower-only mode)
-          if (row_ok && jc + 31 <= i) {
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              atomicAdd(reinterpret_cast<float4*>(hrow + jc + 4 * u),
-                        make_float4(acc[c * 32 + 4 * u], acc[c * 32 + 4 * u + 1], acc[c * 32 + 4 * u + 2],
-                                    acc[c * 32 + 4 * u + 3]));
-          } else {
-#pragma unroll
-            for (int u = 0; u < 32; ++u)
-              if (row_ok && jc + u <= i) atomicAdd(hrow + jc + u, acc[c * 32 + u]);
-          }
-          continue;
-        }
-        if (row_ok && jc + 31 <= i) {
-          // chunk entirely in the lower triangle of this row (and inside the matrix)
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            float4 o = *reinterpret_cast<const float4*>(hrow + jc + 4 * u);
-            o.x += acc[c * 32 + 4 * u];
-            o.y += acc[c * 32 + 4 * u + 1];
-            o.z += acc[c * 32 + 4 * u + 2];
-            o.w += acc[c * 32 + 4 * u + 3];
-            *reinterpret_cast<float4*>(hrow + jc + 4 * u) = o;
-            acc[c * 32 + 4 * u] = o.x; acc[c * 32 + 4 * u + 1] = o.y;
-            acc[c * 32 + 4 * u + 2] = o.z; acc[c * 32 + 4 * u + 3] = o.w;
-          }
-        } else {
-#pragma unroll
-          for (int u = 0; u < 32; ++u) {
-            if (row_ok && jc + u <= i) {
-              acc[c * 32 + u] += hrow[jc + u];
-              hrow[jc + u] = acc[c * 32 + u];
-            }
-          }
-        }
-        if (!p.lower_only) {
-          // mirror: element (i, j), j < i, also goes to (j, i); lanes hold consecutive i
-#pragma unroll
-          for (int u = 0; u < 32; ++u) {
-            const int j = jc + u;
-            if (row_ok && j < i) p.h[(int64_t)j * p.ldh + i] = acc[c * 32 + u];
-          }
-        }
-      }
+      update_h(p, acc, bi * BM + quarter * 32 + lane, bj * BN + half * 128, bi * BM + BM - 1);
     }
   }
 
@@ -288,6 +292,197 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2).  The 1-CTA kernel above is bound by shared-memory bandwidth: per
+// MMA the tensor core reads 12 KB of operands while TMA writes another 12 KB (measured: 1430-1600
+// TFLOP/s with the loads removed, 1190-1220 with them).  Two CTAs of a cluster compute a 256 x 256 tile
+// together: each holds its own 128 rows of A and one half (128 columns) of B, the hardware shares the B
+// halves between the two tensor cores, and the traffic per SM drops to 8 KB + 8 KB per MMA.
+//   both CTAs   producer (TMA into own shared memory, completion counted on the LEADER's full barrier),
+//               epilogue (own 128 rows of the accumulator)
+//   leader only MMA issue; commits are multicast to the barriers of both CTAs
+// No TMA multicast is used: every CTA fetches its own boxes.
+// ---------------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 6;
+constexpr int P_STAGE_BYTES = A_BYTES + B_BYTES / 2;   // 32 KB per CTA: 128 rows of A, 128 columns of B
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_BAND = 8;                              // row blocks (of 256) per band of the tile order
+
+// pair tile t -> (row block bi2, column block bj2 <= bi2) in units of 256, banded like tile_coords
+__device__ __forceinline__ void pair_tile_coords(int t, int first_block, int last_block, int& bi, int& bj) {
+  for (int lo = first_block;; lo += P_BAND) {
+    const int hi = min(lo + P_BAND, last_block);
+    for (int c = 0; c < hi; ++c) {
+      const int first = max(lo, c);
+      const int cnt = hi - first;
+      if (t < cnt) {
+        bi = first + t;
+        bj = c;
+        return;
+      }
+      t -= cnt;
+    }
+    if (hi >= last_block) break;
+  }
+  bi = first_block;
+  bj = 0;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
+  extern __shared__ uint8_t smem_unaligned[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  // same layout in both CTAs: [0..S) full (leader's are used), [S..2S) empty, then tmem_full[2], tmem_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (P_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);    // the leader's expect_tx arrival; bytes of both CTAs
+      mbar_init(empty_bar(s), 1);   // multicast commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);   // multicast commit
+      mbar_init(tempty_bar(b), 16); // 8 epilogue warps of each CTA (leader's barrier is the one waited on)
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anything is signalled remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int k_blocks = (p.tokens + KT - 1) / KT;
+  const int n_work = p.n_tiles * p.ksplit;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) ---------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&xmap);
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+        int t, kbeg, kend, bi, bj;
+        work_range(p, w, k_blocks, t, kbeg, kend);
+        pair_tile_coords(t, p.first_block, p.last_block, bi, bj);
+        const int a_col = bi * 256 + (int)rank * 128, b_col = bj * 256 + (int)rank * 128;
+        for (int kb = kbeg; kb < kend; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * P_STAGE_BYTES);
+          const uint32_t full_leader = map_to_cta(full_bar(s), 0);
+          const uint32_t dst = smem_base + s * P_STAGE_BYTES;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) tma_load_2d_pair(dst + a * BOX_BYTES, &xmap, a_col + 64 * a, kb * KT, full_leader);
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+            tma_load_2d_pair(dst + A_BYTES + b * BOX_BYTES, &xmap, b_col + 64 * b, kb * KT, full_leader);
+          if (++s == P_STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_f16(1 /*bf16*/, 1, 1, 256, BN);
+      int s = 0;
+      uint32_t round = 0, it = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+        int t, kbeg, kend;
+        work_range(p, w, k_blocks, t, kbeg, kend);
+        for (int kb0 = kbeg; kb0 < kend && ok; kb0 += CHUNK_KB, ++it) {
+          const uint32_t buf = it & 1, use = it >> 1;
+          if (!(ok = mbar_wait(tempty_bar(buf), (use & 1) ^ 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int kb1 = min(kb0 + CHUNK_KB, kend);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ++ks) {
+              const uint64_t ad = make_smem_desc(a0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
+              const uint64_t bd = make_smem_desc(b0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
+              umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+            }
+            umma_commit_pair(empty_bar(s), 3);   // frees the stage in both CTAs
+            if (++s == P_STAGES) { s = 0; ++round; }
+          }
+          if (ok) umma_commit_pair(tfull_bar(buf), 3);
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs, own 128 rows) -----------------------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+      int t, kbeg, kend, bi, bj;
+      work_range(p, w, k_blocks, t, kbeg, kend);
+      pair_tile_coords(t, p.first_block, p.last_block, bi, bj);
+      float acc[128];
+#pragma unroll
+      for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
+      for (int kb0 = kbeg; kb0 < kend && ok; kb0 += CHUNK_KB, ++it) {
+        const uint32_t buf = it & 1, use = it >> 1;
+        if (!(ok = mbar_wait(tfull_bar(buf), use & 1, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 32; ++u) acc[c * 32 + u] += __uint_as_float(r[u]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(tempty_bar(buf));
+          else mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        }
+      }
+      if (!ok) break;
+      const int row0 = bi * 256 + (int)rank * 128;
+      update_h(p, acc, row0 + quarter * 32 + lane, bj * 256 + half * 128, row0 + 127);
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves (or frees TMEM) while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
@@ -340,24 +535,62 @@ static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t h
                               (uint64_t)hidden * 2, 64, hess::KT, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != 0) return rc;
 
-  const int b0 = (int)(row_begin / hess::BM), b1 = (int)((row_end + hess::BM - 1) / hess::BM);
+  const int sms = sm_count();
+  // CTA-pair kernel: 256 x 256 tiles, needs row panels aligned to 256 and at least one pair of SMs
+  static const int use_pair = env_int("WUSH_B200_HESSIAN_PAIR", 1);
+  const bool pair = use_pair && row_begin % 256 == 0 && (row_end % 256 == 0 || row_end == hidden) && sms >= 2;
+  const int blk = pair ? 256 : hess::BM;
+  const int b0 = (int)(row_begin / blk), b1 = (int)((row_end + blk - 1) / blk);
   int64_t n_tiles = 0;
-  for (int b = b0; b < b1; ++b) n_tiles += (b >> 1) + 1;
-  // column blocks past the matrix edge never exist: bj <= bi/2 implies bj*256 <= bi*128 < hidden
+  for (int b = b0; b < b1; ++b) n_tiles += pair ? b + 1 : (b >> 1) + 1;
+  // column blocks past the matrix edge never exist: they start at or before their row block
+  const int units = pair ? sms / 2 : sms;   // CTAs (or CTA pairs) working side by side
+
   // Token splits: only in lower-only mode (the mirror needs final values).  Pick the split count that
   // wastes the least of the last wave, keeping at least 1024 tokens per split.
-  const int sms = sm_count();
   int ksplit = 1;
   if (flags & WUSH_HESSIAN_LOWER_ONLY) {
     const int max_split = (int)(tokens / 1024 < 1 ? 1 : (tokens / 1024 > 16 ? 16 : tokens / 1024));
     double best = 1e30;
     for (int ks = 1; ks <= max_split; ++ks) {
-      const double work = (double)n_tiles * ks, waves = (double)((int64_t)(work + sms - 1) / sms);
-      const double cost = waves * sms / work + 0.02 * ks;   // relative time, penalty per extra pass of atomics over H
+      const double work = (double)n_tiles * ks, waves = (double)((int64_t)(work + units - 1) / units);
+      const double cost = waves * units / work + 0.02 * ks;   // relative time, penalty per extra pass of atomics over H
       if (cost < best - 1e-9) { best = cost; ksplit = ks; }
     }
   }
   hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, b1, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+
+  if (pair) {
+    static bool attr_set_pair = false;
+    if (!attr_set_pair) {
+      cudaError_t e = cudaFuncSetAttribute(hess::hessian_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           hess::P_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr_set_pair = true;
+    }
+    // clusters of 2 that can be resident at once (SMs that cannot be paired inside their GPC stay idle)
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * units);
+      cfg.blockDim = dim3(hess::THREADS);
+      cfg.dynamicSmemBytes = hess::P_SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, hess::hessian_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = units;
+      max_pairs = n;
+    }
+    int64_t pairs = max_pairs < units ? max_pairs : units;
+    if (pairs > n_tiles * ksplit) pairs = n_tiles * ksplit;
+    hess::hessian_pair_kernel<<<(unsigned)(2 * pairs), hess::THREADS, hess::P_SMEM_BYTES, stream>>>(map, p);
+    return (int)cudaGetLastError();
+  }
 
   static bool attr_set = false;
   if (!attr_set) {

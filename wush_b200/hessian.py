@@ -58,7 +58,7 @@ def _kernel_finalize(h: torch.Tensor, scale: float) -> None:
     _lib.check(rc, "wush_hessian_finalize")
 
 
-def panel_bounds(hidden: int, panels: int, align: int = 128) -> list[tuple[int, int]]:
+def panel_bounds(hidden: int, panels: int, align: int = 256) -> list[tuple[int, int]]:
     """Row panels of roughly equal lower-triangle area, boundaries on multiples of `align`."""
     cuts = [0]
     for p in range(1, panels):
