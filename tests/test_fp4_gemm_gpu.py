@@ -78,3 +78,22 @@ def test_gemm_linearity_full_size():
     want = wo.fp4_gemm(aq[rows].numpy(), asf[rows].numpy(), bq[cols].numpy(), bsf[cols].numpy(), 1.0, "mxfp4")
     got = y1[rows.to(dev)][:, cols.to(dev)].double().cpu().numpy()
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= TOL
+
+
+def test_gemm_cta_pair_kernel_in_subprocess():
+    """The CTA-pair kernel is off by default and chosen by an environment variable that the library reads
+    once, so it is exercised in a fresh process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from tests.test_fp4_gemm_gpu import _run\n"
+        "for fmt in ('mx', 'nv'):\n"
+        "    for m, n, k in [(256, 256, 512), (200, 328, 384), (1024, 512, 4096)]:\n"
+        "        rel, _, _ = _run(fmt, m, n, k)\n"
+        "        assert rel <= 1e-2, (fmt, m, n, k, rel)\n"
+        "print('pair ok')\n" % os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env = dict(os.environ, WUSH_B200_GEMM_PAIR="1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0 and "pair ok" in out.stdout, out.stdout + out.stderr

@@ -44,7 +44,7 @@ constexpr int B_BYTES = BN * BK / 2;          // 32 KB
 constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4); MXFP4 uses 2
 constexpr int SFB_BYTES = 4096;               // two 128-row blocks
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
 constexpr int THREADS = 448;                  // 14 warps: producer, MMA, 8 epilogue, 4 scale feeders
 constexpr int EPI_WARP0 = 2, SF_WARP0 = 10;
 constexpr uint32_t TMEM_COLS = 512;
@@ -80,6 +80,26 @@ __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint4& a, const
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 template <bool NV>
+__device__ __forceinline__ void umma_fp4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if (NV) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  }
+}
+
+template <bool NV>
 __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   if (NV) {
@@ -101,9 +121,9 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
 
 // Block-scaled instruction descriptor: E2M1 operands (format 1), both K-major, scale format
 // E8M0 (1) or E4M3 (0), K = 64, scale-factor byte offsets (0..3) inside the TMEM columns.
-__device__ __forceinline__ uint32_t make_idesc_fp4(bool nv, uint32_t sf_id) {
+__device__ __forceinline__ uint32_t make_idesc_fp4(bool nv, uint32_t sf_id, uint32_t m = BM) {
   return (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((nv ? 0u : 1u) << 23) |
-         ((uint32_t)(BM >> 4) << 24) | (sf_id << 29);
+         ((m >> 4) << 24) | (sf_id << 29);
 }
 
 // work item -> (m block, n block, split); m fastest so neighbouring CTAs share a weight panel
@@ -119,6 +139,41 @@ __device__ __forceinline__ void split_range(const Params& p, int sp, int& kb0, i
   kb1 = (int)((int64_t)(sp + 1) * p.k_blocks / p.splits);
 }
 
+// Epilogue of one thread: drain its row x 128 accumulator columns as packed bf16 (scaled by alpha),
+// release the accumulator through `release` (after a warp sync), then store to y.
+template <class Release>
+__device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr, float alpha, int row, int col0,
+                                                Release release) {
+  uint32_t packed[64];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int v = 0; v < 16; ++v) {
+      const __nv_bfloat162 h =
+          __floats2bfloat162_rn(__uint_as_float(r[2 * v]) * alpha, __uint_as_float(r[2 * v + 1]) * alpha);
+      packed[c * 16 + v] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  release();
+  if (row >= p.m) return;
+  __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col0;
+  if (col0 + 128 <= p.n) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      *reinterpret_cast<uint4*>(dst + 8 * u) =
+          make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < 64; ++u)       // n % 8 == 0: pairs never straddle the edge
+      if (col0 + 2 * u < p.n) *reinterpret_cast<uint32_t*>(dst + 2 * u) = packed[u];
+  }
+}
+
 template <bool NV>
 __global__ void __launch_bounds__(THREADS, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const Params p) {
@@ -127,8 +182,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  // bars[0..S): full, [S..2S): empty, [2S]: tmem_full, [2S+1]: tmem_empty, [2S+2..3S+2): scales in TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 2);
+  // bars[0..S): full (operands), [S..2S): empty, [2S]: tmem_full, [2S+1]: tmem_empty, [2S+2..3S+2): scales
+  // in TMEM, [3S+2..4S+2): sffull (scale tiles in shared memory)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * STAGES + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -138,11 +194,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
   const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES), tempty_bar = bar_base + 8 * (2 * STAGES + 1);
   auto sf_bar = [&](int s) { return bar_base + 8 * (2 * STAGES + 2 + s); };
+  auto sffull_bar = [&](int s) { return bar_base + 8 * (3 * STAGES + 2 + s); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(sffull_bar(s), 1);
       mbar_init(sf_bar(s), 4);   // one arrival per feeder warp
     }
     mbar_init(tfull_bar, 1);
@@ -178,15 +236,17 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
           const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
           const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES + sf_bytes * (1 + b_blocks));
+          // the small scale tiles get their own barrier so the feeders can start before the operands land
+          mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * (1 + b_blocks));
+          mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
-          tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
-          tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
           bulk_load(dst + A_BYTES + B_BYTES, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
-                    full_bar(s));
+                    sffull_bar(s));
           for (int r = 0; r < b_blocks; ++r)
             bulk_load(dst + A_BYTES + B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
-                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, full_bar(s));
+                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
+          tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
+          tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -243,7 +303,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       work_coords(p, w, mb, nb, sp);
       split_range(p, sp, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(sffull_bar(s), round & 1, abort_flag))) break;
         const uint8_t* sfa = smem + s * STAGE_BYTES + A_BYTES + B_BYTES + lane * 16;
         const uint8_t* sfb = sfa + SFA_BYTES;
         uint4 va[ATOMS], vb[ATOMS][2];
@@ -281,35 +341,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       const int row = mb * BM + quarter * 32 + lane;
       const int col0 = nb * BN + half * 128;
       if (p.splits == 1) {
-        // drain this thread's row x 128 columns as packed bf16, then hand the accumulator back
-        uint32_t packed[64];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int v = 0; v < 16; ++v) {
-            const __nv_bfloat162 h =
-                __floats2bfloat162_rn(__uint_as_float(r[2 * v]) * alpha, __uint_as_float(r[2 * v + 1]) * alpha);
-            packed[c * 16 + v] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar);
-        if (row >= p.m) continue;
-        __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col0;
-        if (col0 + 128 <= p.n) {
-#pragma unroll
-          for (int u = 0; u < 16; ++u)
-            *reinterpret_cast<uint4*>(dst + 8 * u) =
-                make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-        } else {
-#pragma unroll
-          for (int u = 0; u < 64; ++u)       // n % 8 == 0: pairs never straddle the edge
-            if (col0 + 2 * u < p.n) *reinterpret_cast<uint32_t*>(dst + 2 * u) = packed[u];
-        }
+        drain_and_store(p, taddr, alpha, row, col0, [&] {
+          if (lane == 0) mbar_arrive(tempty_bar);
+        });
       } else {
         // split K: fp32 partial tile, stored chunk by chunk before the accumulator is released
         float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col0;
@@ -339,6 +373,202 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2) for M > 128: two CTAs of a cluster compute a 256 x 256 tile.  Each holds
+// its own 128 rows of A (and their scales), one half (128 rows) of B, and the scales of all 256 columns
+// of B.  Per MMA every SM now reads 8 KB of operands and receives 8 KB from TMA instead of 12 + 12, which
+// relieves shared-memory bandwidth.  Measured at 8192^3 it is nevertheless SLOWER than the 1-CTA kernel
+// (2.3 vs 3.9 PFLOP/s): the extra cross-CTA hops (remote barrier arrivals of the peer's feeders and
+// epilogue, multicast commits) lengthen the refill loop of a pipeline that is already latency-bound.  It
+// is kept, off by default (WUSH_B200_GEMM_PAIR=1 enables it), as the starting point for a version with a
+// deeper pipeline.  No TMA multicast: every CTA fetches its own boxes.  Barriers: operand loads of both CTAs count on the leader's `full`; scale copies count on a local
+// `sffull`; feeders of both CTAs arrive on the leader's `sfready`; commits are multicast to both CTAs.
+// ---------------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 5;
+constexpr int P_B_BYTES = B_BYTES / 2;                                   // 128 rows of B
+constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 512;
+
+template <bool NV>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const Params p) {
+  constexpr int GROUP = NV ? 16 : 32;
+  constexpr int ATOMS = BK / GROUP / 4;
+  extern __shared__ uint8_t smem_unaligned[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  // [0,S) full (leader's used)  [S,2S) sffull (local)  [2S,3S) empty  [3S,4S) sfready (leader's used)
+  // [4S] tmem_full  [4S+1] tmem_empty (leader's used)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * P_STAGES + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto sffull_bar = [&](int s) { return bar_base + 8 * (P_STAGES + s); };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (2 * P_STAGES + s); };
+  auto sfready_bar = [&](int s) { return bar_base + 8 * (3 * P_STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8 * (4 * P_STAGES), tempty_bar = bar_base + 8 * (4 * P_STAGES + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(sffull_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(sfready_bar(s), 8);   // 4 feeder warps of each CTA
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 16);        // 8 epilogue warps of each CTA
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int m_blocks2 = (p.m + 255) / 256;
+  const int n_work = m_blocks2 * p.n_blocks;
+  const int sfa_row_blocks = (p.m + 127) / 128;
+
+  if (warp == 0) {
+    // ------------------------------- producer (both CTAs) -------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&amap);
+      tma_prefetch_desc(&bmap);
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+        const int mb2 = w % m_blocks2, nb = w / m_blocks2;
+        const int a_blk = mb2 * 2 + (int)rank;                    // this CTA's 128-row block of A
+        const bool a_sf = a_blk < sfa_row_blocks;                 // rows past M have no scales (and zero data)
+        const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (A_BYTES + P_B_BYTES));
+          mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * ((a_sf ? 1 : 0) + b_blocks));
+          const uint32_t full_leader = map_to_cta(full_bar(s), 0);
+          const uint32_t dst = smem_base + s * P_STAGE_BYTES;
+          tma_load_2d_pair(dst, &amap, kb * (BK / 2), a_blk * 128, full_leader);
+          tma_load_2d_pair(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN + (int)rank * 128, full_leader);
+          if (a_sf)
+            bulk_load(dst + A_BYTES + P_B_BYTES, p.sfa + ((int64_t)a_blk * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
+                      sffull_bar(s));
+          for (int r = 0; r < b_blocks; ++r)
+            bulk_load(dst + A_BYTES + P_B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
+                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
+          if (++s == P_STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader only) ---------------------------------------
+    if (lane == 0 && leader) {
+      int s = 0;
+      uint32_t round = 0, it = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs, ++it) {
+        if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(sfready_bar(s), round & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
+          const int ksteps = atoms * (NV ? 1 : 2);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            const uint64_t ad = make_smem_desc(a0 + ks * 32, 16, 1024, kSwizzle128B);
+            const uint64_t bd = make_smem_desc(b0 + ks * 32, 16, 1024, kSwizzle128B);
+            const int atom = NV ? ks : (ks >> 1);
+            const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
+            umma_fp4_pair<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id, 256), sfa_col + 4 * atom, sfb_col + 8 * atom,
+                              (kb > 0) || (ks != 0));
+          }
+          umma_commit_pair(empty_bar(s), 3);
+          if (++s == P_STAGES) { s = 0; ++round; }
+        }
+        if (ok) umma_commit_pair(tfull_bar, 3);
+      }
+    }
+  } else if (warp >= SF_WARP0) {
+    // ------------------------------- scale feeders (both CTAs) --------------------------------------
+    const int quarter = warp & 3;
+    int s = 0;
+    uint32_t round = 0;
+    bool ok = true;
+    for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!(ok = mbar_wait(sffull_bar(s), round & 1, abort_flag))) break;
+        const uint8_t* sfa = smem + s * P_STAGE_BYTES + A_BYTES + P_B_BYTES + lane * 16;
+        const uint8_t* sfb = sfa + SFA_BYTES;
+        uint4 va[ATOMS], vb[ATOMS][2];
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+          va[a] = *reinterpret_cast<const uint4*>(sfa + a * 512);
+          vb[a][0] = *reinterpret_cast<const uint4*>(sfb + a * 512);
+          vb[a][1] = *reinterpret_cast<const uint4*>(sfb + SFB_BYTES / 2 + a * 512);
+        }
+        const uint32_t sfa_col = tmem_base + ((uint32_t)(quarter * 32) << 16) + SF_COL0 + s * SF_STAGE_COLS;
+#pragma unroll
+        for (int a = 0; a < ATOMS; a += 2) tmem_st_x8(sfa_col + 4 * a, va[a], va[a + 1]);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(sfready_bar(s));
+          else mbar_arrive_cluster(map_to_cta(sfready_bar(s), 0));
+        }
+        if (++s == P_STAGES) { s = 0; ++round; }
+      }
+    }
+  } else if (warp >= EPI_WARP0) {
+    // ------------------------------- epilogue (both CTAs, own 128 rows) -----------------------------
+    const int quarter = warp & 3;
+    const int half = (warp - EPI_WARP0) >> 2;
+    const float alpha = *p.alpha;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = pair_id; w < n_work && ok; w += n_pairs, ++it) {
+      const int mb2 = w % m_blocks2, nb = w / m_blocks2;
+      if (!(ok = mbar_wait(tfull_bar, it & 1, abort_flag))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
+      const int row = mb2 * 256 + (int)rank * 128 + quarter * 32 + lane;
+      drain_and_store(p, taddr, alpha, row, nb * BN + half * 128, [&] {
+        if (lane == 0) {
+          if (leader) mbar_arrive(tempty_bar);
+          else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+        }
+      });
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
@@ -410,6 +640,42 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   rc = make_tensor_map_2d(&bmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
                           BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != 0) return rc;
+
+  // large M, unsplit: 256 x 256 tiles on CTA pairs
+  static const int use_pair = env_int("WUSH_B200_GEMM_PAIR", 0);   // measured slower than the 1-CTA kernel, see above
+  if (use_pair && splits == 1 && m > 128 && sms >= 2) {
+    CUtensorMap bmap2;
+    rc = make_tensor_map_2d(&bmap2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
+                            BK / 2, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return rc;
+    auto pk = nv ? fp4_gemm_pair_kernel<true> : fp4_gemm_pair_kernel<false>;
+    static bool pair_attr_set[2] = {false, false};
+    static int max_pairs[2] = {0, 0};
+    if (!pair_attr_set[nv]) {
+      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * (sms / 2));
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int nmax = 0;
+      if (cudaOccupancyMaxActiveClusters(&nmax, pk, &cfg) != cudaSuccess || nmax <= 0) nmax = sms / 2;
+      max_pairs[nv] = nmax;
+      pair_attr_set[nv] = true;
+    }
+    const int64_t ptiles = ((m + 255) / 256) * (int64_t)p.n_blocks;
+    int64_t pairs = max_pairs[nv] < sms / 2 ? max_pairs[nv] : sms / 2;
+    if (pairs > ptiles) pairs = ptiles;
+    pk<<<(unsigned)(2 * pairs), THREADS, P_SMEM_BYTES, stream>>>(amap, bmap2, p);
+    return (int)cudaGetLastError();
+  }
 
   auto kern = nv ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
   static bool attr_set[2] = {false, false};
