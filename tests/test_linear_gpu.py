@@ -1,0 +1,74 @@
+"""Whole quantized-linear path on the GPU: calibration Hessian -> WUSH matrices -> weight codes (CPU oracle, the
+reference's RTN recipe) -> FPQuantLinear.forward = fused transform+quantize + FP4 GEMM, against the CPU oracle of
+the same pipeline (1e-2 relative Frobenius) and, as a sanity bound, against the unquantized bf16 product."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import synth
+from oracle import wush_oracle as wo
+
+pytestmark = pytest.mark.gpu
+
+
+def _wush_setup(hidden, rows_out, fmt, dev):
+    from wush_b200.hessian import DistributedHessian
+    g = wo.FORMATS[fmt]["group"]
+    calib = [synth.activations(512, hidden, seed=80 + i) for i in range(2)]
+    dh = DistributedHessian(hidden, dev)
+    for c in calib:
+        dh.update(c.to(dev))
+    h = dh.finalize().double().cpu().numpy()
+    h[np.diag_indices(hidden)] += 1e-2 * np.trace(h) / hidden            # wush_gptq.py:197-199
+    basis = np.linalg.cholesky(h).T                                       # upper: basis^T basis = h
+    w = synth.bf16_to_f64(synth.weights(rows_out, hidden, seed=5))
+    y = basis @ w.T
+    t = np.stack([wo.get_transform(basis[i:i + g, i:i + g], y[i:i + g], "wush") for i in range(0, hidden, g)])
+    # weight side of the transform: W_n T_n^-1 per group, then RTN (force_rtn path of quantize_layers)
+    wt = np.concatenate([w[:, n * g:(n + 1) * g] @ np.linalg.inv(t[n]) for n in range(hidden // g)], axis=1)
+    wq = wo.rtn_xxfp4(wt, fmt)
+    return w, t, wq
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_wush_linear_end_to_end(fmt):
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    hidden, rows_out, tokens = 1024, 512, 200
+    g = wo.FORMATS[fmt]["group"]
+    w, t, wq = _wush_setup(hidden, rows_out, fmt, dev)
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=g, transform_init="wush")
+    layer = FPQuantLinear(hidden, rows_out, cfg, bias=True, device=dev)
+    mat = wo.transform_to_matrix(t)
+    layer.load_quantized(torch.from_numpy(wq["e2m1"]), torch.from_numpy(wq["scale_quant"]), torch.from_numpy(mat))
+    bias = torch.linspace(-1, 1, rows_out, dtype=torch.bfloat16, device=dev)
+    layer.bias.data.copy_(bias)
+    x = synth.activations(tokens, hidden, seed=90)
+    y = layer(x.to(dev).view(2, tokens // 2, hidden))
+    torch.cuda.synchronize()
+    assert y.shape == (2, tokens // 2, rows_out) and y.dtype == torch.bfloat16
+    got = y.double().cpu().numpy().reshape(tokens, rows_out)
+    xq = wo.fused_transform_quant(synth.bf16_to_f64(x), mat, fmt)
+    gs = wo.FORMATS[fmt]["global_scale"]
+    want = wo.fp4_gemm(xq["e2m1"], xq["scale_quant"], wq["e2m1"], wq["scale_quant"], 1.0 / (gs * gs), fmt)
+    want = want + bias.double().cpu().numpy()[None, :]
+    assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
+    exact = synth.bf16_to_f64(x) @ w.T + bias.double().cpu().numpy()[None, :]
+    rel = np.linalg.norm(got - exact) / np.linalg.norm(exact)
+    assert rel < 0.25, rel                      # W4A4 quantization error, not a kernel tolerance
+
+
+def test_hadamard_linear_quantizes_its_own_weight():
+    from wush_b200.linear import FPQuantConfig, FPQuantLinear
+    dev = torch.device("cuda:0")
+    layer = FPQuantLinear(512, 256, FPQuantConfig(), bias=False, device=dev)
+    w = synth.weights(256, 512, seed=6)
+    layer.weight.data.copy_(w.to(dev))
+    layer.pre_forward()
+    assert layer.weight is None and layer.qweight.shape == (256, 256) and layer.scales.shape == (256, 16)
+    x = synth.activations(64, 512, seed=7)
+    y = layer(x.to(dev)).double().cpu().numpy()
+    exact = synth.bf16_to_f64(x) @ synth.bf16_to_f64(w).T
+    assert np.linalg.norm(y - exact) / np.linalg.norm(exact) < 0.25
+    with pytest.raises(NotImplementedError):
+        FPQuantConfig(forward_method="quest") and FPQuantLinear(512, 256, FPQuantConfig(forward_method="quest"), device=dev)
