@@ -143,8 +143,14 @@ __device__ __forceinline__ void quantize_row(float (&v)[8], float gs, float gs6,
     // ulp at most.  A zero scale gives inf, hence +-6 / NaN codes, as the oracle's division does.
     mul = __fdividef(gs, e4m3_value(scale_byte));
   }
+  // packed fp32 multiplies: two products per instruction (each product is rounded on its own)
+  const float2 m2 = make_float2(mul, mul);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] *= mul;
+  for (int i = 0; i < 8; i += 2) {
+    const float2 pr = __fmul2_rn(make_float2(v[i], v[i + 1]), m2);
+    v[i] = pr.x;
+    v[i + 1] = pr.y;
+  }
   packed = pack_e2m1x8(v);
   if (!NV && amax == 0.0f) packed = 0x88888888u;  // the reference encodes an all-zero group as -0
 }
@@ -223,15 +229,28 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
   // this lane copies piece q4 of rows g, g+8, g+16, g+24 of every tile
   const uint32_t ring_wr = smem_base + warp * (kStageBytes / kWarps) + g * 64 + ((q4 ^ ((g >> 1) & 3)) << 4);
+  // Tiles are issued strictly in order, so the producer side keeps a running stage offset, a running
+  // row and a running source pointer instead of multiplying per tile.
+  uint32_t issue_stage_off = 0;
+  int issue_row = row_begin + g;                                   // first of this lane's 4 rows of the next tile
+  const __nv_bfloat16* issue_ptr = xcol + (int64_t)issue_row * p.cols;
+  const int64_t row8 = 8 * p.cols, row32 = 32 * p.cols;           // element strides of 8 and 32 rows
   auto issue_tile = [&](int t) {
     if (active && t < n_tiles) {
-      const int r0 = row_begin + t * kTileRows + g;
-      const uint32_t dst = ring_wr + (uint32_t)(t % kStages) * kStageBytes;
+      const uint32_t dst = ring_wr + issue_stage_off;
+      if (issue_row + 24 <= last_row) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = min(r0 + 8 * i, last_row);  // clamp: rows past the end are discarded later
-        cp_async_16(dst + i * (8 * 64), xcol + (int64_t)r * p.cols);
+        for (int i = 0; i < 4; ++i) cp_async_16(dst + i * (8 * 64), issue_ptr + i * row8);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = min(issue_row + 8 * i, last_row);  // clamp: rows past the end are discarded later
+          cp_async_16(dst + i * (8 * 64), xcol + (int64_t)r * p.cols);
+        }
       }
+      issue_row += kTileRows;
+      issue_ptr += row32;
+      issue_stage_off = issue_stage_off + kStageBytes == kRingBytes ? 0u : issue_stage_off + kStageBytes;
     }
     cp_async_commit();
   };
@@ -317,6 +336,26 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   const int sf_slab0 = (int)(slab_col0 / TD);           // first scale group of the slab
   const int sf_total = (int)(p.cols / TD);
 
+  // loop-invariant ldmatrix offsets inside a stage: [mt][ks]
+  uint32_t a_off[2][2];
+  {
+    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      const int r = arow + 16 * mt;
+      const int sw = (r >> 1) & 3;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks)
+        a_off[mt][ks] = warp * (kStageBytes / kWarps) + r * 64 + ((((lane >> 4) + 2 * ks) ^ sw) << 4);
+    }
+  }
+  uint32_t use_stage_off = 0;
+  const int64_t q_tile_stride = (int64_t)kTileRows * q_stride;
+  // staging offsets of this lane's 4 rows of a tile
+  const int out_q_lane = g * kOutRow + warp * 16 + q4 * 4;
+  const int out_sf_lane = g * kSfRow + (NV ? warp * 2 + (q4 >> 1) : warp);
+  const bool sf_writer = NV ? (q4 & 1) == 0 : q4 == 0;
+
   for (int t = 0; t < n_tiles; ++t) {
     issue_tile(t + kStages - 1);
     cp_async_wait<kStages - 1>();
@@ -327,18 +366,13 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
     if (active) {
       __syncwarp();  // the tile was copied by all lanes of this warp
       // A fragments: rows (lane%8) + 8*((lane/8)%2) of a 16-row tile, 16-byte piece (lane/16) + 2ks
-      const uint32_t tile = smem_base + (uint32_t)(t % kStages) * kStageBytes + warp * (kStageBytes / kWarps);
-      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const uint32_t tile = smem_base + use_stage_off;
+      use_stage_off = use_stage_off + kStageBytes == kRingBytes ? 0u : use_stage_off + kStageBytes;
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {  // two 16-row MMA tiles: rows g+16mt and g+8+16mt
         uint32_t a0[4], a1[4];
-        {
-          const int r = arow + 16 * mt;
-          const uint32_t rowaddr = tile + r * 64;
-          const int sw = (r >> 1) & 3;
-          ldmatrix_x4(a0, rowaddr + ((((lane >> 4) + 0) ^ sw) << 4));
-          ldmatrix_x4(a1, rowaddr + ((((lane >> 4) + 2) ^ sw) << 4));
-        }
+        ldmatrix_x4(a0, tile + a_off[mt][0]);
+        ldmatrix_x4(a1, tile + a_off[mt][1]);
         float acc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -365,12 +399,8 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
           }
           uint32_t packed, sbyte;
           quantize_row<NV>(v, gs, gs6, packed, sbyte);
-          *reinterpret_cast<uint32_t*>(out_q + trow * kOutRow + warp * 16 + q4 * 4) = packed;
-          if (NV) {
-            if ((q4 & 1) == 0) out_sf[trow * kSfRow + warp * 2 + (q4 >> 1)] = (uint8_t)sbyte;
-          } else {
-            if (q4 == 0) out_sf[trow * kSfRow + warp] = (uint8_t)sbyte;
-          }
+          *reinterpret_cast<uint32_t*>(out_q + out_q_lane + (trow - g) * kOutRow) = packed;
+          if (sf_writer) out_sf[out_sf_lane + (trow - g) * kSfRow] = (uint8_t)sbyte;
         }
       }
     }
@@ -379,8 +409,9 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
     // ---- coalesced stores: each row of the slab is 128 contiguous bytes of codes ------------
     if (st_ok && r0 + st_row < row_end) {
       const uint4 v = *reinterpret_cast<const uint4*>(out_q + st_row * kOutRow + st_seg * 16);
-      *reinterpret_cast<uint4*>(q_dst + (int64_t)t * kTileRows * q_stride) = v;
+      *reinterpret_cast<uint4*>(q_dst) = v;
     }
+    q_dst += q_tile_stride;
     if (warp == 0) {
       const int row = r0 + lane;
       if (row < row_end) {
@@ -416,7 +447,11 @@ template <bool NV, bool DEBUG, bool RB, bool BL>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
   const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
-  static const int waves = env_int("WUSH_B200_QUANT_WAVES", 2);
+  // Waves of resident CTAs: narrow matrices (few slabs) do best in a single wave, wide ones in three
+  // (measured at 16384 rows: 4096 channels 4470/4240/3970 GB/s for 1/2/3 waves, 14336 channels
+  // 4930/5170/5200).  WUSH_B200_QUANT_WAVES overrides the choice.
+  static const int waves_env = env_int("WUSH_B200_QUANT_WAVES", 0);
+  const int waves = waves_env > 0 ? waves_env : (slabs <= 16 ? 1 : (slabs <= 32 ? 2 : 3));
   const int64_t resident = (int64_t)sm_count() * WUSH_Q_MINBLOCKS;
   int64_t splits = (resident * waves) / slabs;
   if (splits < 1) splits = 1;
