@@ -145,6 +145,26 @@ WUSH_API int wush_hessian_accumulate_rows(float* h, const void* x, int64_t token
  * the 1/N factor on every call; applying it once here is algebraically the same).  hidden % 4 == 0.
  */
 WUSH_API int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* stream);
+/* The same with scale = 1 / *count, `count` being a device int64 (e.g. the all-reduced token count): keeps a
+ * multi-GPU job free of host synchronisation.  No counterpart in the reference, which is single-GPU. */
+WUSH_API int wush_hessian_finalize_count(float* h, int64_t hidden, const int64_t* count, void* stream);
+
+/*
+ * Multi-GPU combine of the Hessian over peer memory (one process per GPU, NVLink / NVSwitch).
+ * No counterpart in the reference, which is single-GPU.
+ *
+ *   bufs    DEVICE array of `world` pointers: every rank's fp32 [hidden, hidden] buffer holding its raw
+ *           lower-triangle sum, all addressable from this GPU (e.g. torch symmetric memory)
+ *   counts  DEVICE array of `world` pointers to each rank's int64 local token count (peer-addressable)
+ * On return (stream order) every rank's buffer holds, for the 32x32 tiles this rank owns (tile t belongs to
+ * rank t % world), the sum over ranks divided by the total token count, lower triangle and mirror image.
+ * Once EVERY rank has run it, all buffers hold the complete symmetric matrix, bit-identical on all ranks.
+ * The caller must separate the launches from the producers and consumers of the buffers with cross-rank
+ * barriers: all ranks' partial sums complete before any rank starts, all ranks done before the result is
+ * read.  hidden % 4 == 0, world <= 16.
+ */
+WUSH_API int wush_hessian_peer_reduce(float* const* bufs, const int64_t* const* counts, int rank, int world,
+                                      int64_t hidden, void* stream);
 
 /*
  * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.

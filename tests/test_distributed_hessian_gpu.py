@@ -33,30 +33,49 @@ def test_single_gpu_update_and_overlapped():
     assert a.num_samples == b.num_samples == 3648
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, peer):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      WUSH_B200_HESSIAN_PEER="1" if peer else "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     from wush_b200.hessian import DistributedHessian
     x = synth.activations(1024 + 256 * rank, 1024, seed=70 + rank).to(dev)
     dh = DistributedHessian(1024, dev, panels=4)
+    assert (dh._peer is not None) == peer
     dh.accumulate_overlapped(x)
     h = dh.finalize()
     torch.cuda.synchronize()
+    assert dh.num_samples == sum(1024 + 256 * r for r in range(world))
+    # every rank must hold the same bits
+    mine = h.clone()
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(mine, ref)
     if rank == 0:
         np.save(out, h.cpu().numpy())
+    dh.release()
+    # second job on the pooled buffer (update path)
+    dh2 = DistributedHessian(1024, dev)
+    dh2.update(x[:512])
+    dh2.update(x[512:])
+    h2 = dh2.finalize()
+    torch.cuda.synchronize()
+    assert (h2 - mine).abs().max() <= 1e-5 * mine.abs().max()
     dist.barrier()
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_nccl(tmp_path):
+@pytest.mark.parametrize("peer", [True, False])
+def test_two_gpu_hessian(tmp_path, peer):
+    """peer=True: ranks combined by the peer-memory kernel; False: NCCL all-reduce of row panels."""
     import torch.multiprocessing as mp
     out = str(tmp_path / "h.npy")
-    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300 + (7 if peer else 0), out, peer), nprocs=2, join=True)
     got = np.load(out).astype(np.float64)
     want = wo.wush_update_sequence([synth.bf16_to_f64(synth.activations(1024 + 256 * r, 1024, seed=70 + r)) for r in range(2)])
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    assert np.array_equal(got, got.T)

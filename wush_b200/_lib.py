@@ -57,6 +57,8 @@ def load() -> ctypes.CDLL:
         "wush_hessian_accumulate": [vp, vp, i64, i64, i32, vp, vp],
         "wush_hessian_accumulate_rows": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
         "wush_hessian_finalize": [vp, i64, ctypes.c_float, vp],
+        "wush_hessian_finalize_count": [vp, i64, vp, vp],
+        "wush_hessian_peer_reduce": [vp, vp, i32, i32, i64, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
     }

@@ -610,8 +610,10 @@ namespace hess {
 // Lower triangle (already summed) -> scaled lower triangle and its mirror image, 32 x 32 tiles:
 // a block reads tile (bi, bj), bj <= bi, scales it in place and writes its transpose to (bj, bi)
 // through shared memory, so both the reads and the mirrored writes are coalesced.
-__global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale, int64_t tiles_per_side) {
+__global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale, const long long* __restrict__ count,
+                                int64_t tiles_per_side) {
   __shared__ float tile[32][33];
+  if (count) scale = 1.0f / (float)(*count > 0 ? *count : 1);   // token count produced on the device (all-reduce)
   const int64_t n_tiles = tiles_per_side * (tiles_per_side + 1) / 2;
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     // t -> (bi, bj) with bj <= bi
@@ -653,7 +655,18 @@ extern "C" int wush_hessian_accumulate_rows(float* h, const void* x, int64_t tok
   return hessian_launch(h, x, tokens, hidden, row_begin, row_end, flags, status, (cudaStream_t)stream);
 }
 
+static int hessian_finalize(float* h, int64_t hidden, float scale, const long long* count, void* stream);
+
 extern "C" int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* stream) {
+  return hessian_finalize(h, hidden, scale, nullptr, stream);
+}
+
+extern "C" int wush_hessian_finalize_count(float* h, int64_t hidden, const int64_t* count, void* stream) {
+  if (!count) return WUSH_ERR_NULL_POINTER;
+  return hessian_finalize(h, hidden, 0.0f, reinterpret_cast<const long long*>(count), stream);
+}
+
+static int hessian_finalize(float* h, int64_t hidden, float scale, const long long* count, void* stream) {
   if (!h) return WUSH_ERR_NULL_POINTER;
   if (hidden <= 0 || hidden % 4 != 0) return WUSH_ERR_BAD_SHAPE;
   if ((uintptr_t)h & 15) return WUSH_ERR_BAD_ALIGNMENT;
@@ -661,6 +674,6 @@ extern "C" int wush_hessian_finalize(float* h, int64_t hidden, float scale, void
   int64_t blocks = side * (side + 1) / 2;
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  hess::finalize_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, scale, side);
+  hess::finalize_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, scale, count, side);
   return (int)cudaGetLastError();
 }

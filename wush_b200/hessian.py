@@ -58,6 +58,49 @@ def _kernel_finalize(h: torch.Tensor, scale: float) -> None:
     _lib.check(rc, "wush_hessian_finalize")
 
 
+def _kernel_finalize_count(h: torch.Tensor, count: torch.Tensor) -> None:
+    with torch.cuda.device(h.device):
+        rc = _lib.load().wush_hessian_finalize_count(h.data_ptr(), h.shape[0], count.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "wush_hessian_finalize_count")
+
+
+class _PeerBuffers:
+    """A Hessian buffer in symmetric (peer-addressable) memory plus the device-side pointer tables the
+    peer-reduce kernel needs.  Creating one is a collective over the group; instances are pooled and
+    reused because the rendezvous costs milliseconds."""
+
+    _pool: dict = {}
+
+    def __init__(self, hidden: int, device: torch.device, group):
+        import os
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        # plain peer loads/stores only: do not bind the buffer to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        grp = group if group is not None else dist.group.WORLD
+        n = hidden * hidden
+        self.flat = symm.empty(n + 4, dtype=torch.float32, device=device)      # 16 spare bytes: int64 token count
+        self.handle = symm.rendezvous(self.flat, group=grp)
+        self.h = self.flat[:n].view(hidden, hidden)
+        self.count = self.flat[n:n + 2].view(torch.int64)
+        ptrs = [int(x) for x in self.handle.buffer_ptrs]
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.buf_table = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.count_table = torch.tensor([x + 4 * n for x in ptrs], dtype=torch.int64, device=device)
+        self.key = (hidden, device.index, id(grp))
+
+    @classmethod
+    def acquire(cls, hidden: int, device: torch.device, group):
+        import torch.distributed as dist
+        grp = group if group is not None else dist.group.WORLD
+        free = cls._pool.setdefault((hidden, device.index, id(grp)), [])
+        return free.pop() if free else cls(hidden, device, group)
+
+    def release(self) -> None:
+        self._pool.setdefault(self.key, []).append(self)
+
+
 def panel_bounds(hidden: int, panels: int, align: int = 256) -> list[tuple[int, int]]:
     """Row panels of roughly equal lower-triangle area, boundaries on multiples of `align`."""
     cuts = [0]
@@ -87,11 +130,30 @@ class DistributedHessian:
     (gloo) with a stand-in for the CUDA kernels; the defaults call the kernels and need a GPU.
     """
 
-    def __init__(self, hidden: int, device, group=None, panels: int = 4, accumulate_fn=None, finalize_fn=None):
+    def __init__(self, hidden: int, device, group=None, panels: int = 4, accumulate_fn=None, finalize_fn=None,
+                 peer: bool | None = None):
+        import os
         import torch.distributed as dist
         self.hidden, self.device, self.group, self.panels = hidden, torch.device(device), group, panels
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
-        self.raw = torch.zeros(hidden, hidden, dtype=torch.float32, device=self.device)
+        # Multi-GPU on CUDA: keep the sum in peer-addressable memory and combine the ranks with the
+        # peer-reduce kernel (NVLink loads/stores, fused with scaling and mirror).  peer=False, the
+        # environment switch WUSH_B200_HESSIAN_PEER=0, injected stand-in functions or a failed
+        # symmetric-memory set-up select the NCCL all-reduce of row panels instead.
+        if peer is None:
+            peer = os.environ.get("WUSH_B200_HESSIAN_PEER", "1") != "0"
+        self._peer = None
+        if peer and self.world > 1 and self.device.type == "cuda" and accumulate_fn is None and finalize_fn is None:
+            try:
+                self._peer = _PeerBuffers.acquire(hidden, self.device, group)
+            except Exception as exc:   # symmetric memory not available for this group/device
+                import warnings
+                warnings.warn(f"peer-memory Hessian reduce unavailable ({exc}); using NCCL all-reduce")
+        if self._peer is not None:
+            self.raw = self._peer.h
+            self.raw.zero_()
+        else:
+            self.raw = torch.zeros(hidden, hidden, dtype=torch.float32, device=self.device)
         self.local_tokens = 0
         self._reduced = False
         self._accumulate = accumulate_fn or _kernel_accumulate
@@ -113,10 +175,11 @@ class DistributedHessian:
         x = x.reshape(-1, x.shape[-1])
         assert not self._reduced
         cuda = self._comm_stream is not None
-        if self.world == 1:
+        if self.world == 1 or self._peer is not None:
+            # one launch over all local tokens; with peer memory the ranks are combined in finalize()
             self._accumulate(self.raw, x, 0, self.hidden, True)
             self.local_tokens += x.shape[0]
-            self._reduced = True
+            self._reduced = self._peer is None
             return
         for (r0, r1) in panel_bounds(self.hidden, self.panels):
             self._accumulate(self.raw, x, r0, r1, True)
@@ -145,6 +208,19 @@ class DistributedHessian:
     def finalize(self) -> torch.Tensor:
         import torch.distributed as dist
         total = self.local_tokens
+        if self._peer is not None:
+            pb = self._peer
+            pb.count.fill_(self.local_tokens)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            pb.handle.barrier(channel=0)          # every rank's partial sum and count are complete
+            with torch.cuda.device(self.device):
+                rc = _lib.load().wush_hessian_peer_reduce(pb.buf_table.data_ptr(), pb.count_table.data_ptr(), pb.rank,
+                                                          pb.world, self.hidden, stream)
+            _lib.check(rc, "wush_hessian_peer_reduce")
+            pb.handle.barrier(channel=1)          # every rank has delivered its tiles everywhere
+            self._reduced = True
+            self._count = None                    # total is computed on demand (num_samples)
+            return self.raw
         if self.world > 1:
             if not self._reduced:
                 for (r0, r1) in panel_bounds(self.hidden, self.panels):
@@ -152,7 +228,30 @@ class DistributedHessian:
                 self._reduced = True
             n = torch.tensor([self.local_tokens], dtype=torch.int64, device=self.device)
             dist.all_reduce(n, group=self.group)
+            self._count = n
+            if self._finalize is _kernel_finalize:
+                # the count stays on the device: no host synchronisation inside the job
+                _kernel_finalize_count(self.raw, n)
+                return self.raw
             total = int(n.item())
         self._finalize(self.raw, 1.0 / max(total, 1))
-        self.num_samples = total
+        self._count = total
         return self.raw
+
+    @property
+    def num_samples(self) -> int:
+        """Tokens over all ranks (reads the device-side count if the reduction left it there)."""
+        c = getattr(self, "_count", self.local_tokens)
+        if c is None:
+            import torch.distributed as dist
+            n = torch.tensor([self.local_tokens], dtype=torch.int64, device=self.device)
+            dist.all_reduce(n, group=self.group)
+            c = self._count = int(n.item())
+        return int(c.item()) if isinstance(c, torch.Tensor) else int(c)
+
+    def release(self) -> None:
+        """Give a peer-memory buffer back to the pool (the matrix returned by finalize() is then reused by
+        the next DistributedHessian of the same size).  No-op for ordinary buffers."""
+        if self._peer is not None:
+            self._peer.release()
+            self._peer = None
