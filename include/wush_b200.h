@@ -110,6 +110,8 @@ WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, i
 
 /* flags of wush_hessian_accumulate */
 #define WUSH_HESSIAN_LOWER_ONLY 1 /* update the lower triangle (and diagonal) only, do not mirror */
+#define WUSH_HESSIAN_INPUT_F32 2  /* x is fp32 [tokens, hidden]; products are formed in TF32 (top 19 bits of each
+                                     operand), as the reference's Triton kernel does for fp32 inputs */
 
 /*
  * GPTQ Hessian accumulation, in place:  H += X^T X.
@@ -119,8 +121,8 @@ WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, i
  * src/quantization/wush_gptq.py:456-469).
  *
  *   h       fp32 [hidden, hidden] row-major, 16-byte aligned, read and written
- *   x       bf16 [tokens, hidden] row-major, 16-byte aligned, hidden % 8 == 0
- *   flags   0, or WUSH_HESSIAN_LOWER_ONLY (the reference's save_lower_only=True)
+ *   x       bf16 (or fp32 with WUSH_HESSIAN_INPUT_F32) [tokens, hidden] row-major, 16-byte aligned, hidden % 8 == 0
+ *   flags   bitwise OR of WUSH_HESSIAN_LOWER_ONLY (the reference's save_lower_only=True) and WUSH_HESSIAN_INPUT_F32
  *   status  optional device int, set to 1 if a bounded wait inside the kernel ran out (the result
  *           is then invalid); may be NULL
  * bf16 products are exact in fp32 and are summed in fp32 tensor-core accumulators over the tokens

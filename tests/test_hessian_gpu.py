@@ -69,3 +69,37 @@ def test_meta_batch_and_errors():
         accumulate_hessian(h.cpu(), x.cpu())
     with pytest.raises(NotImplementedError):
         accumulate_hessian(h, x.half())
+
+
+def _tf32(x: np.ndarray, mode: str) -> np.ndarray:
+    """float32 values reduced to TF32's 10 mantissa bits, by truncation or round-to-nearest-even."""
+    b = x.astype(np.float32).view(np.uint32).astype(np.uint64)
+    if mode == "trunc":
+        b = b & 0xFFFFE000
+    else:
+        b = (b + 0xFFF + ((b >> 13) & 1)) & 0xFFFFE000
+    return b.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+@pytest.mark.parametrize("tokens,hidden", [(300, 256), (2048, 1024), (40000, 128)])
+def test_hessian_fp32_input_uses_tf32_products(tokens, hidden):
+    """fp32 activations (what the reference's WUSH.update passes): TF32 products, fp32 accumulation.  Checked
+    loosely against the exact float64 result (TF32 keeps 10 mantissa bits) and tightly against a float64
+    accumulation of TF32-reduced inputs."""
+    from wush_b200.hessian import accumulate_hessian
+    dev = torch.device("cuda:0")
+    x = synth.activations(tokens, hidden, seed=7, dtype=torch.float32) * 0.37     # not bf16-representable
+    h = torch.zeros(hidden, hidden, device=dev)
+    accumulate_hessian(h, x.to(dev))
+    torch.cuda.synchronize()
+    got = h.cpu().double().numpy()
+    x64 = x.double().numpy()
+    exact = x64.T @ x64
+    assert np.abs(got - exact).max() <= 2e-3 * np.abs(exact).max()
+    errs = []
+    for mode in ("trunc", "rne"):
+        xt = _tf32(x.numpy(), mode)
+        ref = xt.T @ xt
+        errs.append(np.abs(got - ref).max() / np.abs(ref).max())
+    assert min(errs) <= 2e-5, errs
+    assert np.array_equal(got, got.T)

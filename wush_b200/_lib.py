@@ -22,6 +22,7 @@ ERRORS = {
 SF_ROW_MAJOR, SF_BLOCKED = 0, 1
 QUANT_ROUND_BF16 = 1
 HESSIAN_LOWER_ONLY = 1
+HESSIAN_INPUT_F32 = 2
 
 _lib = None
 

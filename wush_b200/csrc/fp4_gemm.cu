@@ -392,7 +392,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
 constexpr int P_STAGES = 5;
 constexpr int P_B_BYTES = B_BYTES / 2;                                   // 128 rows of B
 constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 512;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 512;   // barriers: 5 * P_STAGES + 2 words of 8 bytes
 
 template <bool NV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
@@ -403,8 +403,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
   // [0,S) full (leader's used)  [S,2S) sffull (local)  [2S,3S) empty  [3S,4S) sfready (leader's used)
-  // [4S] tmem_full  [4S+1] tmem_empty (leader's used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * P_STAGES + 2);
+  // [4S] tmem_full  [4S+1] tmem_empty (leader's used)  [4S+2,5S+2) sflocal (peer's used)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 * P_STAGES + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -418,13 +418,15 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
   auto empty_bar = [&](int s) { return bar_base + 8 * (2 * P_STAGES + s); };
   auto sfready_bar = [&](int s) { return bar_base + 8 * (3 * P_STAGES + s); };
   const uint32_t tfull_bar = bar_base + 8 * (4 * P_STAGES), tempty_bar = bar_base + 8 * (4 * P_STAGES + 1);
+  auto sflocal_bar = [&](int s) { return bar_base + 8 * (4 * P_STAGES + 2 + s); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(sffull_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(sfready_bar(s), 8);   // 4 feeder warps of each CTA
+      mbar_init(sfready_bar(s), 5);   // the leader's 4 feeder warps + one relayed arrival for the peer's four
+      mbar_init(sflocal_bar(s), 4);   // peer CTA: its feeder warps; a relay thread forwards the completion
     }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, 16);        // 8 epilogue warps of each CTA
@@ -507,6 +509,19 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         }
         if (ok) umma_commit_pair(tfull_bar, 3);
       }
+    } else if (lane == 0) {
+      // peer CTA: this otherwise idle thread relays "the peer's scales are in TMEM" to the leader with ONE
+      // cluster-scope arrival per stage (remote arrivals are expensive; the feeders arrive locally)
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(sflocal_bar(s), round & 1, abort_flag))) break;
+          mbar_arrive_cluster(map_to_cta(sfready_bar(s), 0));
+          if (++s == P_STAGES) { s = 0; ++round; }
+        }
+      }
     }
   } else if (warp >= SF_WARP0) {
     // ------------------------------- scale feeders (both CTAs) --------------------------------------
@@ -534,10 +549,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          if (leader) mbar_arrive(sfready_bar(s));
-          else mbar_arrive_cluster(map_to_cta(sfready_bar(s), 0));
-        }
+        if (lane == 0) mbar_arrive(leader ? sfready_bar(s) : sflocal_bar(s));
         if (++s == P_STAGES) { s = 0; ++round; }
       }
     }

@@ -35,15 +35,31 @@ namespace hess {
 using namespace sm100;
 
 constexpr int BM = 128, BN = 256;   // output tile
-constexpr int KT = 64;              // tokens per pipeline stage
 constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * KT * 2;          // 16 KB: two 64-channel boxes
-constexpr int B_BYTES = BN * KT * 2;          // 32 KB: four 64-channel boxes
+// Element-type dependent geometry.  bf16: boxes of 64 channels x 64 tokens, K = 16 per MMA (kind::f16);
+// fp32 input: boxes of 32 channels x 32 tokens, K = 8 per MMA (kind::tf32 -- the tensor core uses the top
+// 19 bits of each operand, which is what the reference's Triton kernel does with fp32 inputs).  Either way
+// a box row is 128 bytes, a stage holds 16 KB of A and 32 KB of B and feeds 4 MMAs.
+template <bool F32>
+struct Elem {
+  static constexpr int BYTES = F32 ? 4 : 2;
+  static constexpr int BOXC = 128 / BYTES;        // channels per TMA box
+  static constexpr int KT = F32 ? 32 : 64;        // tokens per pipeline stage
+  static constexpr int KMMA = F32 ? 8 : 16;       // tokens per MMA
+  static constexpr int KSTEP_BYTES = KMMA * 128;  // descriptor advance per MMA
+  static constexpr int BOX_BYTES = 128 * KT;      // one box: BOXC channels x KT tokens
+  // Shared-memory layout the MMA descriptor names.  16-bit operands: 128-byte swizzle on 16-byte units,
+  // repeating every 8 tokens (1024 bytes).  MN-major 32-bit operands are transposed in 32-byte units, so
+  // they use the 128-byte swizzle on 32-byte units, which repeats every 4 tokens (512 bytes).
+  static constexpr uint64_t DESC_SWIZZLE = F32 ? 1 /*128B, 32-byte base*/ : 2 /*128B*/;
+  static constexpr uint32_t SBO = F32 ? 512 : 1024;
+};
+constexpr int A_BYTES = BM * 64 * 2;          // 16 KB
+constexpr int B_BYTES = BN * 64 * 2;          // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int BOX_BYTES = 64 * KT * 2;        // one box: 64 channels x KT tokens
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 320;
-constexpr int CHUNK_KB = 8;                  // k-blocks (of KT tokens) summed in one TMEM accumulator: 512 tokens
+constexpr int CHUNK_KB = 8;                  // k-blocks summed in one TMEM accumulator: 512 (bf16) / 256 (fp32) tokens
 constexpr uint32_t TMEM_COLS = 512;
 
 struct Params {
@@ -150,7 +166,10 @@ __device__ __forceinline__ void update_h(const Params& p, float (&acc)[128], int
   }
 }
 
+template <bool F32>
 __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
+  using E = Elem<F32>;
+  constexpr int KT = E::KT, BOX_BYTES = E::BOX_BYTES;
   extern __shared__ uint8_t smem_unaligned[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
@@ -207,10 +226,11 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
 #pragma unroll
-          for (int a = 0; a < BM / 64; ++a) tma_load_2d(dst + a * BOX_BYTES, &xmap, bi * BM + 64 * a, kb * KT, full_bar(s));
+          for (int a = 0; a < BM / E::BOXC; ++a)
+            tma_load_2d(dst + a * BOX_BYTES, &xmap, bi * BM + E::BOXC * a, kb * KT, full_bar(s));
 #pragma unroll
-          for (int b = 0; b < BN / 64; ++b)
-            tma_load_2d(dst + A_BYTES + b * BOX_BYTES, &xmap, bj * BN + 64 * b, kb * KT, full_bar(s));
+          for (int b = 0; b < BN / E::BOXC; ++b)
+            tma_load_2d(dst + A_BYTES + b * BOX_BYTES, &xmap, bj * BN + E::BOXC * b, kb * KT, full_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -218,7 +238,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -----------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(1 /*bf16*/, 1, 1, BM, BN);
+      constexpr uint32_t idesc = make_idesc_f16(F32 ? 2 /*tf32*/ : 1 /*bf16*/, 1, 1, BM, BN);
       int s = 0;
       uint32_t round = 0, it = 0;  // it counts chunks: accumulator buffer = it & 1
       bool ok = true;
@@ -236,12 +256,13 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
             tc_fence_after();
             const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < KT / 16; ++ks) {
-              // MN-major, 128-byte swizzle: 64-channel atoms are BOX_BYTES apart (leading offset),
-              // 8-token groups 1024 bytes apart (stride offset); 16 tokens = 2048 bytes per MMA
-              const uint64_t ad = make_smem_desc(a0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
-              const uint64_t bd = make_smem_desc(b0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
-              umma_f16(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+            for (int ks = 0; ks < KT / E::KMMA; ++ks) {
+              // MN-major, 128-byte swizzle: channel atoms (128 bytes wide) are BOX_BYTES apart (leading
+              // offset), 8-token groups 1024 bytes apart (stride offset); one MMA spans KMMA tokens
+              const uint64_t ad = make_smem_desc(a0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+              const uint64_t bd = make_smem_desc(b0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+              if (F32) umma_tf32(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+              else umma_f16(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
             }
             umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
             if (++s == STAGES) { s = 0; ++round; }
@@ -333,8 +354,11 @@ __device__ __forceinline__ void pair_tile_coords(int t, int first_block, int las
   bj = 0;
 }
 
+template <bool F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
+  using E = Elem<F32>;
+  constexpr int KT = E::KT, BOX_BYTES = E::BOX_BYTES;
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
@@ -396,10 +420,11 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
           const uint32_t full_leader = map_to_cta(full_bar(s), 0);
           const uint32_t dst = smem_base + s * P_STAGE_BYTES;
 #pragma unroll
-          for (int a = 0; a < 2; ++a) tma_load_2d_pair(dst + a * BOX_BYTES, &xmap, a_col + 64 * a, kb * KT, full_leader);
+          for (int a = 0; a < 128 / E::BOXC; ++a)
+            tma_load_2d_pair(dst + a * BOX_BYTES, &xmap, a_col + E::BOXC * a, kb * KT, full_leader);
 #pragma unroll
-          for (int b = 0; b < 2; ++b)
-            tma_load_2d_pair(dst + A_BYTES + b * BOX_BYTES, &xmap, b_col + 64 * b, kb * KT, full_leader);
+          for (int b = 0; b < 128 / E::BOXC; ++b)
+            tma_load_2d_pair(dst + A_BYTES + b * BOX_BYTES, &xmap, b_col + E::BOXC * b, kb * KT, full_leader);
           if (++s == P_STAGES) { s = 0; ++round; }
         }
       }
@@ -407,7 +432,7 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_f16(1 /*bf16*/, 1, 1, 256, BN);
+      constexpr uint32_t idesc = make_idesc_f16(F32 ? 2 /*tf32*/ : 1 /*bf16*/, 1, 1, 256, BN);
       int s = 0;
       uint32_t round = 0, it = 0;
       bool ok = true;
@@ -425,10 +450,11 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
             tc_fence_after();
             const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < KT / 16; ++ks) {
-              const uint64_t ad = make_smem_desc(a0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
-              const uint64_t bd = make_smem_desc(b0 + ks * 2048, BOX_BYTES, 1024, kSwizzle128B);
-              umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+            for (int ks = 0; ks < KT / E::KMMA; ++ks) {
+              const uint64_t ad = make_smem_desc(a0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+              const uint64_t bd = make_smem_desc(b0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+              if (F32) umma_tf32_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
+              else umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
             }
             umma_commit_pair(empty_bar(s), 3);   // frees the stage in both CTAs
             if (++s == P_STAGES) { s = 0; ++round; }
@@ -511,7 +537,7 @@ static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidde
   for (int64_t t0 = 0; t0 < tokens; t0 += kSegmentTokens) {
     const int64_t n = tokens - t0 < kSegmentTokens + kSegmentTokens / 2 ? tokens - t0 : kSegmentTokens;
     const bool last = t0 + n >= tokens;
-    const int rc = hessian_launch_one(h, xb + t0 * hidden * 2, n, hidden, row_begin, row_end,
+    const int rc = hessian_launch_one(h, xb + t0 * hidden * ((flags & WUSH_HESSIAN_INPUT_F32) ? 4 : 2), n, hidden, row_begin, row_end,
                                       last ? flags : (flags | WUSH_HESSIAN_LOWER_ONLY), status, stream);
     if (rc != 0) return rc;
     if (last) break;
@@ -526,13 +552,18 @@ static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t h
   if (row_begin < 0 || row_end > hidden || row_begin > row_end || row_begin % hess::BM != 0 ||
       (row_end % hess::BM != 0 && row_end != hidden))
     return WUSH_ERR_BAD_SHAPE;
-  if (flags & ~WUSH_HESSIAN_LOWER_ONLY) return WUSH_ERR_BAD_FLAG;
+  if (flags & ~(WUSH_HESSIAN_LOWER_ONLY | WUSH_HESSIAN_INPUT_F32)) return WUSH_ERR_BAD_FLAG;
+  const bool f32 = (flags & WUSH_HESSIAN_INPUT_F32) != 0;
   if (((uintptr_t)h & 15) || ((uintptr_t)x & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   if (tokens == 0 || row_begin == row_end) return WUSH_OK;
 
   CUtensorMap map;
-  int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
-                              (uint64_t)hidden * 2, 64, hess::KT, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = f32 ? make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, (uint64_t)tokens, (uint64_t)hidden,
+                                    (uint64_t)hidden * 4, hess::Elem<true>::BOXC, hess::Elem<true>::KT,
+                                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+               : make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
+                                    (uint64_t)hidden * 2, hess::Elem<false>::BOXC, hess::Elem<false>::KT,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != 0) return rc;
 
   const int sms = sm_count();
@@ -561,12 +592,12 @@ static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t h
   hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, b1, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
 
   if (pair) {
-    static bool attr_set_pair = false;
-    if (!attr_set_pair) {
-      cudaError_t e = cudaFuncSetAttribute(hess::hessian_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           hess::P_SMEM_BYTES);
+    auto pk = f32 ? hess::hessian_pair_kernel<true> : hess::hessian_pair_kernel<false>;
+    static bool attr_set_pair[2] = {false, false};
+    if (!attr_set_pair[f32]) {
+      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, hess::P_SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      attr_set_pair = true;
+      attr_set_pair[f32] = true;
     }
     // clusters of 2 that can be resident at once (SMs that cannot be paired inside their GPC stay idle)
     static int max_pairs = 0;
@@ -583,25 +614,25 @@ static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t h
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, hess::hessian_pair_kernel, &cfg) != cudaSuccess || n <= 0) n = units;
+      if (cudaOccupancyMaxActiveClusters(&n, pk, &cfg) != cudaSuccess || n <= 0) n = units;
       max_pairs = n;
     }
     int64_t pairs = max_pairs < units ? max_pairs : units;
     if (pairs > n_tiles * ksplit) pairs = n_tiles * ksplit;
-    hess::hessian_pair_kernel<<<(unsigned)(2 * pairs), hess::THREADS, hess::P_SMEM_BYTES, stream>>>(map, p);
+    pk<<<(unsigned)(2 * pairs), hess::THREADS, hess::P_SMEM_BYTES, stream>>>(map, p);
     return (int)cudaGetLastError();
   }
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(hess::hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         hess::SMEM_BYTES);
+  auto k1 = f32 ? hess::hessian_kernel<true> : hess::hessian_kernel<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[f32]) {
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, hess::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_set[f32] = true;
   }
   int grid = sms;
   if (grid > n_tiles * ksplit) grid = (int)(n_tiles * ksplit);
-  hess::hessian_kernel<<<grid, hess::THREADS, hess::SMEM_BYTES, stream>>>(map, p);
+  k1<<<grid, hess::THREADS, hess::SMEM_BYTES, stream>>>(map, p);
   return (int)cudaGetLastError();
 }
 

@@ -15,7 +15,8 @@ def accumulate_hessian(mat_hessian: torch.Tensor, mat_input: torch.Tensor, save_
     """In place ``mat_hessian += mat_input^T @ mat_input``; returns ``mat_hessian``.
 
     mat_hessian: ([meta,] hidden, hidden) fp32, contiguous, on a CUDA device.
-    mat_input:   ([meta,] tokens, hidden) bf16, contiguous.
+    mat_input:   ([meta,] tokens, hidden) bf16, or fp32 (then the products are formed in TF32, like the
+                 reference's kernel when its caller passes fp32), contiguous.
     save_lower_only: update only the lower triangle (incl. diagonal) and leave the rest untouched.
     compute_lower_only: kept for signature compatibility; the kernel always computes the lower
         triangle and mirrors it, which gives the same (symmetric) result.
@@ -26,8 +27,8 @@ def accumulate_hessian(mat_hessian: torch.Tensor, mat_input: torch.Tensor, save_
         raise _lib.WushB200Error("accumulate_hessian needs CUDA tensors; there is no CPU fallback")
     if mat_hessian.dtype != torch.float32:
         raise ValueError("mat_hessian must be float32")
-    if mat_input.dtype != torch.bfloat16:
-        raise NotImplementedError(f"mat_input dtype {mat_input.dtype}: the kernel takes bfloat16 activations")
+    if mat_input.dtype not in (torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"mat_input dtype {mat_input.dtype}: the kernel takes bfloat16 or float32 activations")
     *meta, tokens, hidden = mat_input.shape
     if tuple(mat_hessian.shape) != (*meta, hidden, hidden):
         raise ValueError(f"shape mismatch: hessian {tuple(mat_hessian.shape)} vs input {tuple(mat_input.shape)}")
@@ -35,6 +36,8 @@ def accumulate_hessian(mat_hessian: torch.Tensor, mat_input: torch.Tensor, save_
     x3 = mat_input.view(-1, tokens, hidden)
     lib = _lib.load()
     flags = _lib.HESSIAN_LOWER_ONLY if save_lower_only else 0
+    if mat_input.dtype == torch.float32:
+        flags |= _lib.HESSIAN_INPUT_F32
     with torch.cuda.device(mat_input.device):
         stream = torch.cuda.current_stream().cuda_stream
         for b in range(h3.shape[0]):
