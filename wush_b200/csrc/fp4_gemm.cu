@@ -139,11 +139,36 @@ __device__ __forceinline__ void split_range(const Params& p, int sp, int& kb0, i
   kb1 = (int)((int64_t)(sp + 1) * p.k_blocks / p.splits);
 }
 
-// Epilogue of one thread: drain its row x 128 accumulator columns as packed bf16 (scaled by alpha),
-// release the accumulator through `release` (after a warp sync), then store to y.
+// 8 x 8 transposition of 16-byte chunks inside every group of 8 lanes: three butterfly stages that swap bit b
+// of the lane index with bit b of the chunk index.  Chunk slot 8h+i of lane (g, j) ends up holding chunk 8h+j
+// of lane (g, i), so that the 8 lanes of a group own one whole 128-byte line per slot.
+__device__ __forceinline__ void transpose_chunks_8x8(uint32_t (&v)[64], int lane) {
+#pragma unroll
+  for (int b = 0; b < 3; ++b) {
+    const int m = 1 << b;
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      if (c & m) continue;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t& lo = v[4 * c + w];
+        uint32_t& hi = v[4 * (c | m) + w];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, upper ? lo : hi, m);
+        if (upper) lo = recv; else hi = recv;
+      }
+    }
+  }
+}
+
+// Epilogue of one warp: every lane drains its row x 128 accumulator columns as packed bf16 (scaled by alpha)
+// and the accumulator is released through `release` (after a warp sync).  A lane-per-row store would touch 32
+// different lines per instruction (4096 L1 wavefronts per tile, which was measured to stall the scale feeders
+// and the next tile's first loads behind it), so the chunks are transposed among groups of 8 lanes first:
+// every store instruction then writes 4 rows x 128 contiguous bytes.  `row0` is the row of lane 0.
 template <class Release>
-__device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr, float alpha, int row, int col0,
-                                                Release release) {
+__device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr, float alpha, int row0, int col0,
+                                                int lane, Release release) {
   uint32_t packed[64];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -160,17 +185,18 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
   tc_fence_before();
   __syncwarp();
   release();
-  if (row >= p.m) return;
-  __nv_bfloat16* dst = p.y + (int64_t)row * p.n + col0;
-  if (col0 + 128 <= p.n) {
+  transpose_chunks_8x8(packed, lane);
+  const int j = lane & 7, rbase = row0 + (lane & ~7);
 #pragma unroll
-    for (int u = 0; u < 16; ++u)
-      *reinterpret_cast<uint4*>(dst + 8 * u) =
-          make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-  } else {
+  for (int h = 0; h < 2; ++h) {
+    const int col = col0 + (8 * h + j) * 8;          // n % 8 == 0: a chunk never straddles the edge
 #pragma unroll
-    for (int u = 0; u < 64; ++u)       // n % 8 == 0: pairs never straddle the edge
-      if (col0 + 2 * u < p.n) *reinterpret_cast<uint32_t*>(dst + 2 * u) = packed[u];
+    for (int i = 0; i < 8; ++i) {
+      const int row = rbase + i, slot = 8 * h + i;
+      if (row < p.m && col < p.n)
+        *reinterpret_cast<uint4*>(p.y + (int64_t)row * p.n + col) =
+            make_uint4(packed[4 * slot], packed[4 * slot + 1], packed[4 * slot + 2], packed[4 * slot + 3]);
+    }
   }
 }
 
@@ -341,7 +367,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       const int row = mb * BM + quarter * 32 + lane;
       const int col0 = nb * BN + half * 128;
       if (p.splits == 1) {
-        drain_and_store(p, taddr, alpha, row, col0, [&] {
+        drain_and_store(p, taddr, alpha, row - lane, col0, lane, [&] {
           if (lane == 0) mbar_arrive(tempty_bar);
         });
       } else {
@@ -566,7 +592,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
       const int row = mb2 * 256 + (int)rank * 128 + quarter * 32 + lane;
-      drain_and_store(p, taddr, alpha, row, nb * BN + half * 128, [&] {
+      drain_and_store(p, taddr, alpha, row - lane, nb * BN + half * 128, lane, [&] {
         if (lane == 0) {
           if (leader) mbar_arrive(tempty_bar);
           else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
