@@ -119,6 +119,47 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
   }
 }
 
+// The four MMAs of a full k-block in one instruction sequence, preceded by a non-blocking test of the
+// barrier the NEXT k-block will wait on.  A barrier test costs the issuing thread ~200 cycles even when the
+// phase is complete, and the MMA queue is shallow: with the test between two k-blocks the tensor pipe ran
+// dry for that long in every k-block.  Placed here its latency overlaps the issue of the MMAs; only the
+// result is consumed afterwards.  Returns whether the probed phase is complete.
+template <bool NV, bool PAIR>
+__device__ __forceinline__ bool umma_fp4_x4_probe(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t idesc_even,
+                                                  uint32_t idesc_odd, uint32_t sfa_col, uint32_t sfb_col,
+                                                  uint32_t accumulate, uint32_t probe_bar, uint32_t probe_parity) {
+  // k-step ks: operands advance 32 bytes (2 descriptor units); MXFP4 uses scale bytes (ks & 1) * 2 of atom
+  // ks >> 1, NVFP4 all four bytes of atom ks
+  const uint32_t a1 = NV ? 1 : 0, a2 = NV ? 2 : 1, a3 = NV ? 3 : 1;
+  uint32_t ready;
+#define WUSH_MMA4(GROUP, KIND)                                                                                     \
+  asm volatile(                                                                                                    \
+      "{\n.reg .pred p, q, t;\n"                                                                                   \
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%21], %22;\n"                                                 \
+      "setp.ne.b32 p, %20, 0;\n"                                                                                   \
+      "setp.eq.b32 t, 0, 0;\n"                                                                                     \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %2, %6, %10, [%12], [%16], p;\n"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %3, %7, %11, [%13], [%17], t;\n"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %4, %8, %10, [%14], [%18], t;\n"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %5, %9, %11, [%15], [%19], t;\n"                      \
+      "selp.u32 %0, 1, 0, q;\n}\n"                                                                                 \
+      : "=r"(ready)                                                                                                \
+      : "r"(d_tmem), "l"(ad), "l"(ad + 2), "l"(ad + 4), "l"(ad + 6), "l"(bd), "l"(bd + 2), "l"(bd + 4),            \
+        "l"(bd + 6), "r"(idesc_even), "r"(idesc_odd), "r"(sfa_col), "r"(sfa_col + 4 * a1), "r"(sfa_col + 4 * a2),  \
+        "r"(sfa_col + 4 * a3), "r"(sfb_col), "r"(sfb_col + 8 * a1), "r"(sfb_col + 8 * a2), "r"(sfb_col + 8 * a3),  \
+        "r"(accumulate), "r"(probe_bar), "r"(probe_parity)                                                         \
+      : "memory")
+  if (NV) {
+    if (PAIR) WUSH_MMA4("2", "mxf4nvf4.block_scale.block16");
+    else WUSH_MMA4("1", "mxf4nvf4.block_scale.block16");
+  } else {
+    if (PAIR) WUSH_MMA4("2", "mxf4.block_scale.block32");
+    else WUSH_MMA4("1", "mxf4.block_scale.block32");
+  }
+#undef WUSH_MMA4
+  return ready != 0;
+}
+
 // Block-scaled instruction descriptor: E2M1 operands (format 1), both K-major, scale format
 // E8M0 (1) or E4M3 (0), K = 64, scale-factor byte offsets (0..3) inside the TMEM columns.
 __device__ __forceinline__ uint32_t make_idesc_fp4(bool nv, uint32_t sf_id, uint32_t m = BM) {
@@ -282,7 +323,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     if (lane == 0) {
       int s = 0;
       uint32_t round = 0, it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;   // ready: the probe issued with the previous k-block saw this one complete
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
         int mb, nb, sp, kb0, kb1;
         work_coords(p, w, mb, nb, sp);
@@ -290,23 +331,30 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
         tc_fence_after();
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+          // one wait per k-block: the feeders arrive on sf_bar only after the operands have landed too
+          if (!ready && !(ok = mbar_wait(sf_bar(s), round & 1, abort_flag))) break;
           tc_fence_after();
           const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
-          if (!(ok = mbar_wait(sf_bar(s), round & 1, abort_flag))) break;   // this stage's scales are in TMEM
-          tc_fence_after();
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
           // atom a of A sits in columns sfa_col + 4a, of B (two 128-row blocks) in sfb_col + 8a + 4r
           const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
-          const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in this k-block
-          for (int ks = 0; ks < ksteps; ++ks) {
-            // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; 64 elements = 32 bytes
-            const uint64_t ad = make_smem_desc(a0 + ks * 32, 16, 1024, kSwizzle128B);
-            const uint64_t bd = make_smem_desc(b0 + ks * 32, 16, 1024, kSwizzle128B);
-            const int atom = NV ? ks : (ks >> 1);
-            const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
-            umma_fp4<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id), sfa_col + 4 * atom, sfb_col + 8 * atom,
-                         (kb > kb0) || (ks != 0));
+          // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; 64 elements = 32 bytes
+          const uint64_t ad = make_smem_desc(a0, 16, 1024, kSwizzle128B);
+          const uint64_t bd = make_smem_desc(b0, 16, 1024, kSwizzle128B);
+          const int sn = (s + 1 == STAGES) ? 0 : s + 1;
+          const uint32_t parity_n = (sn == 0 ? round + 1 : round) & 1;
+          if (atoms == ATOMS) {
+            ready = umma_fp4_x4_probe<NV, false>(tmem_base, ad, bd, make_idesc_fp4(NV, 0), make_idesc_fp4(NV, NV ? 0 : 2),
+                                                 sfa_col, sfb_col, kb > kb0, sf_bar(sn), parity_n);
+          } else {
+            const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in a short last k-block
+            for (int ks = 0; ks < ksteps; ++ks) {
+              const int atom = NV ? ks : (ks >> 1);
+              const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
+              umma_fp4<NV>(tmem_base, ad + 2 * ks, bd + 2 * ks, make_idesc_fp4(NV, sf_id), sfa_col + 4 * atom,
+                           sfb_col + 8 * atom, (kb > kb0) || (ks != 0));
+            }
+            ready = false;
           }
           umma_commit(empty_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
@@ -346,6 +394,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
         tmem_st_wait();
         tc_fence_before();
+        // the MMA issuer waits on sf_bar alone, so it must also imply "operands landed"
+        if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(sf_bar(s));
         if (++s == STAGES) { s = 0; ++round; }
@@ -510,25 +560,35 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
     if (lane == 0 && leader) {
       int s = 0;
       uint32_t round = 0, it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (int w = pair_id; w < n_work && ok; w += n_pairs, ++it) {
         if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
         tc_fence_after();
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
-          if (!(ok = mbar_wait(sfready_bar(s), round & 1, abort_flag))) break;
+          // one wait per k-block: the leader's feeders arrive on sfready only after the operands of both CTAs
+          // have landed (they wait on `full` first)
+          if (!ready && !(ok = mbar_wait(sfready_bar(s), round & 1, abort_flag))) break;
           tc_fence_after();
           const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
           const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
-          const int ksteps = atoms * (NV ? 1 : 2);
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const uint64_t ad = make_smem_desc(a0 + ks * 32, 16, 1024, kSwizzle128B);
-            const uint64_t bd = make_smem_desc(b0 + ks * 32, 16, 1024, kSwizzle128B);
-            const int atom = NV ? ks : (ks >> 1);
-            const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
-            umma_fp4_pair<NV>(tmem_base, ad, bd, make_idesc_fp4(NV, sf_id, 256), sfa_col + 4 * atom, sfb_col + 8 * atom,
-                              (kb > 0) || (ks != 0));
+          const uint64_t ad = make_smem_desc(a0, 16, 1024, kSwizzle128B);
+          const uint64_t bd = make_smem_desc(b0, 16, 1024, kSwizzle128B);
+          const int sn = (s + 1 == P_STAGES) ? 0 : s + 1;
+          const uint32_t parity_n = (sn == 0 ? round + 1 : round) & 1;
+          if (atoms == ATOMS) {
+            ready = umma_fp4_x4_probe<NV, true>(tmem_base, ad, bd, make_idesc_fp4(NV, 0, 256),
+                                                make_idesc_fp4(NV, NV ? 0 : 2, 256), sfa_col, sfb_col, kb > 0,
+                                                sfready_bar(sn), parity_n);
+          } else {
+            const int ksteps = atoms * (NV ? 1 : 2);
+            for (int ks = 0; ks < ksteps; ++ks) {
+              const int atom = NV ? ks : (ks >> 1);
+              const uint32_t sf_id = NV ? 0u : (uint32_t)(ks & 1) * 2u;
+              umma_fp4_pair<NV>(tmem_base, ad + 2 * ks, bd + 2 * ks, make_idesc_fp4(NV, sf_id, 256), sfa_col + 4 * atom,
+                                sfb_col + 8 * atom, (kb > 0) || (ks != 0));
+            }
+            ready = false;
           }
           umma_commit_pair(empty_bar(s), 3);
           if (++s == P_STAGES) { s = 0; ++round; }
@@ -544,7 +604,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
       for (int w = pair_id; w < n_work && ok; w += n_pairs) {
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!(ok = mbar_wait(sflocal_bar(s), round & 1, abort_flag))) break;
-          mbar_arrive_cluster(map_to_cta(sfready_bar(s), 0));
+          mbar_arrive_cluster_relaxed(map_to_cta(sfready_bar(s), 0));
           if (++s == P_STAGES) { s = 0; ++round; }
         }
       }
@@ -574,6 +634,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
         tmem_st_wait();
         tc_fence_before();
+        if (leader && !(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(leader ? sfready_bar(s) : sflocal_bar(s));
         if (++s == P_STAGES) { s = 0; ++round; }
@@ -594,8 +655,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
       const int row = mb2 * 256 + (int)rank * 128 + quarter * 32 + lane;
       drain_and_store(p, taddr, alpha, row - lane, nb * BN + half * 128, lane, [&] {
         if (lane == 0) {
+          // the accumulator reads are complete (tcgen05.wait::ld), nothing travels through memory: the
+          // relaxed remote arrival avoids the ~1600-cycle release fence
           if (leader) mbar_arrive(tempty_bar);
-          else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+          else mbar_arrive_cluster_relaxed(map_to_cta(tempty_bar, 0));
         }
       });
     }

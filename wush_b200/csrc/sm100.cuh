@@ -152,6 +152,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
 }
+// Same without the release fence, for signals whose payload does not travel through memory (e.g. "scales are in
+// tensor memory", already complete after tcgen05.wait::st).  The releasing form was measured at ~1600 cycles
+// per arrival inside a CTA with TMA traffic in flight, which made a per-k-block relay the bottleneck.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
 // TMA tile load into this CTA's shared memory whose completion is counted on an mbarrier that may live
 // in the other CTA of the pair (no multicast: every CTA fetches its own tile)
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
