@@ -45,8 +45,8 @@ constexpr int SFA_BYTES = 2048;               // up to 4 atoms of 512 B (NVFP4);
 constexpr int SFB_BYTES = 4096;               // two 128-row blocks
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
-constexpr int THREADS = 448;                  // 14 warps: producer, MMA, 8 epilogue, 4 scale feeders
-constexpr int EPI_WARP0 = 2, SF_WARP0 = 10;
+constexpr int THREADS = 480;                  // 15 warps: producer, MMA, 8 epilogue, 4 scale feeders, scale producer
+constexpr int EPI_WARP0 = 2, SF_WARP0 = 10, SFP_WARP = 14;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
@@ -299,21 +299,39 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         split_range(p, sp, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
-          // scale atoms really present in this k-block (the last block may hold fewer)
-          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-          const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
-          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-          // the small scale tiles get their own barrier so the feeders can start before the operands land
-          mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * (1 + b_blocks));
           mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
-          bulk_load(dst + A_BYTES + B_BYTES, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
-                    sffull_bar(s));
-          for (int r = 0; r < b_blocks; ++r)
-            bulk_load(dst + A_BYTES + B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
-                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
           tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
           tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == SFP_WARP) {
+    // ------------------------------- scale producer -------------------------------------------------
+    // The three small copies per k-block have a thread of their own: issued by the operand producer they
+    // made its loop (a barrier wait and seven asynchronous operations per k-block) the slowest stage of
+    // the pipeline.  The scale tiles use their own barrier, so the feeders can start before the operands land.
+    if (lane == 0) {
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        int mb, nb, sp, kb0, kb1;
+        work_coords(p, w, mb, nb, sp);
+        split_range(p, sp, kb0, kb1);
+        const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          // scale atoms really present in this k-block (the last block may hold fewer)
+          const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
+          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+          mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * (1 + b_blocks));
+          const uint32_t dst = smem_base + s * STAGE_BYTES + A_BYTES + B_BYTES;
+          bulk_load(dst, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
+          for (int r = 0; r < b_blocks; ++r)
+            bulk_load(dst + SFA_BYTES + r * (SFB_BYTES / 2),
+                      p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -362,7 +380,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (ok) umma_commit(tfull_bar);
       }
     }
-  } else if (warp >= SF_WARP0) {
+  } else if (warp >= SF_WARP0 && warp < SFP_WARP) {
     // ------------------------------- scale feeders ------------------------------------------------
     // Lane l of every feeder reads row l of each 128 x 4 scale atom from shared memory (16 bytes =
     // 4 columns: one per 32-row group, 4 consecutive k-scales per column) and stores it to its own
@@ -455,26 +473,36 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
 
 
 // ---------------------------------------------------------------------------------------------------
-// CTA-pair variant (cta_group::2) for M > 128: two CTAs of a cluster compute a 256 x 256 tile.  Each holds
-// its own 128 rows of A (and their scales), one half (128 rows) of B, and the scales of all 256 columns
-// of B.  Per MMA every SM now reads 8 KB of operands and receives 8 KB from TMA instead of 12 + 12, which
-// relieves shared-memory bandwidth.  Measured at 8192^3 it is nevertheless SLOWER than the 1-CTA kernel
-// (2.3 vs 3.9 PFLOP/s): the extra cross-CTA hops (remote barrier arrivals of the peer's feeders and
-// epilogue, multicast commits) lengthen the refill loop of a pipeline that is already latency-bound.  It
-// is kept, off by default (WUSH_B200_GEMM_PAIR=1 enables it), as the starting point for a version with a
-// deeper pipeline.  No TMA multicast: every CTA fetches its own boxes.  Barriers: operand loads of both CTAs count on the leader's `full`; scale copies count on a local
-// `sffull`; feeders of both CTAs arrive on the leader's `sfready`; commits are multicast to both CTAs.
+// CTA-pair kernel (cta_group::2), the default for M > 128: two CTAs of a cluster compute a 256 x 256 tile.
+// Each holds its own 128 rows of A (and their scales), one half (128 rows) of B, and the scales of all 256
+// columns of B.  Per k-block every SM now receives 32 KB of operands instead of 48: the 1-CTA kernel is bound
+// by the L2 -> SM feed (about 15 TB/s over 148 SMs), this one is not.  No TMA multicast: every CTA fetches its
+// own boxes.  Barriers: operand loads of both CTAs count on the leader's `full`; scale copies count on a local
+// `sffull`; the leader's feeders arrive on its `sfready` (after `full`), the peer's on a local barrier that one
+// relay thread forwards with a relaxed cluster-scope arrival (a releasing remote arrival costs ~1600 cycles
+// with TMA traffic in flight and had made this kernel half as fast as the 1-CTA one); commits are multicast to
+// both CTAs.  WUSH_B200_GEMM_PAIR=0 selects the 1-CTA kernel for every shape.
 // ---------------------------------------------------------------------------------------------------
-constexpr int P_STAGES = 5;
 constexpr int P_B_BYTES = B_BYTES / 2;                                   // 128 rows of B
-constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 512;   // barriers: 5 * P_STAGES + 2 words of 8 bytes
+// Stage geometry by format: MXFP4 has half the scale bytes of NVFP4 per k-block, which buys a sixth stage.
+template <bool NV>
+struct PairGeom {
+  static constexpr int SFA_B = NV ? 2048 : 1024;                 // scale tile of A: 4 / 2 atoms of 512 B
+  static constexpr int SFB_B = NV ? 4096 : 2048;                 // two 128-row blocks of B scales
+  static constexpr int STAGES = NV ? 5 : 6;
+  static constexpr int STAGE_BYTES = A_BYTES + P_B_BYTES + SFA_B + SFB_B;      // 38 KB / 35 KB
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 512;               // barriers: 5 * STAGES + 2 words
+  static constexpr uint32_t SF_COLS = NV ? 48 : 24;              // TMEM columns of one stage's scales
+  static constexpr uint32_t SFB_COL = NV ? 16 : 8;               // where the B scales start inside them
+};
 
 template <bool NV>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const Params p) {
   constexpr int GROUP = NV ? 16 : 32;
   constexpr int ATOMS = BK / GROUP / 4;
+  using G = PairGeom<NV>;
+  constexpr int P_STAGES = G::STAGES, P_STAGE_BYTES = G::STAGE_BYTES;
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
@@ -533,23 +561,38 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
       for (int w = pair_id; w < n_work && ok; w += n_pairs) {
         const int mb2 = w % m_blocks2, nb = w / m_blocks2;
         const int a_blk = mb2 * 2 + (int)rank;                    // this CTA's 128-row block of A
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (A_BYTES + P_B_BYTES));
+          const uint32_t full_leader = map_to_cta(full_bar(s), 0);
+          const uint32_t dst = smem_base + s * P_STAGE_BYTES;
+          tma_load_2d_pair(dst, &amap, kb * (BK / 2), a_blk * 128, full_leader);
+          tma_load_2d_pair(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN + (int)rank * 128, full_leader);
+          if (++s == P_STAGES) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == SFP_WARP) {
+    // ------------------------------- scale producer (both CTAs) -------------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int w = pair_id; w < n_work && ok; w += n_pairs) {
+        const int mb2 = w % m_blocks2, nb = w / m_blocks2;
+        const int a_blk = mb2 * 2 + (int)rank;
         const bool a_sf = a_blk < sfa_row_blocks;                 // rows past M have no scales (and zero data)
         const int b_blocks = min(2, p.sfb_row_blocks - nb * 2);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
           const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (A_BYTES + P_B_BYTES));
           mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * ((a_sf ? 1 : 0) + b_blocks));
-          const uint32_t full_leader = map_to_cta(full_bar(s), 0);
-          const uint32_t dst = smem_base + s * P_STAGE_BYTES;
-          tma_load_2d_pair(dst, &amap, kb * (BK / 2), a_blk * 128, full_leader);
-          tma_load_2d_pair(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN + (int)rank * 128, full_leader);
+          const uint32_t dst = smem_base + s * P_STAGE_BYTES + A_BYTES + P_B_BYTES;
           if (a_sf)
-            bulk_load(dst + A_BYTES + P_B_BYTES, p.sfa + ((int64_t)a_blk * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes,
-                      sffull_bar(s));
+            bulk_load(dst, p.sfa + ((int64_t)a_blk * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
           for (int r = 0; r < b_blocks; ++r)
-            bulk_load(dst + A_BYTES + P_B_BYTES + SFA_BYTES + r * (SFB_BYTES / 2),
+            bulk_load(dst + G::SFA_B + r * (G::SFB_B / 2),
                       p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
           if (++s == P_STAGES) { s = 0; ++round; }
         }
@@ -571,7 +614,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
           tc_fence_after();
           const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
-          const uint32_t sfa_col = tmem_base + SF_COL0 + s * SF_STAGE_COLS, sfb_col = sfa_col + SFB_OFF;
+          const uint32_t sfa_col = tmem_base + SF_COL0 + s * G::SF_COLS, sfb_col = sfa_col + G::SFB_COL;
           const uint64_t ad = make_smem_desc(a0, 16, 1024, kSwizzle128B);
           const uint64_t bd = make_smem_desc(b0, 16, 1024, kSwizzle128B);
           const int sn = (s + 1 == P_STAGES) ? 0 : s + 1;
@@ -609,7 +652,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         }
       }
     }
-  } else if (warp >= SF_WARP0) {
+  } else if (warp >= SF_WARP0 && warp < SFP_WARP) {
     // ------------------------------- scale feeders (both CTAs) --------------------------------------
     const int quarter = warp & 3;
     int s = 0;
@@ -619,19 +662,19 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!(ok = mbar_wait(sffull_bar(s), round & 1, abort_flag))) break;
         const uint8_t* sfa = smem + s * P_STAGE_BYTES + A_BYTES + P_B_BYTES + lane * 16;
-        const uint8_t* sfb = sfa + SFA_BYTES;
+        const uint8_t* sfb = sfa + G::SFA_B;
         uint4 va[ATOMS], vb[ATOMS][2];
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a) {
           va[a] = *reinterpret_cast<const uint4*>(sfa + a * 512);
           vb[a][0] = *reinterpret_cast<const uint4*>(sfb + a * 512);
-          vb[a][1] = *reinterpret_cast<const uint4*>(sfb + SFB_BYTES / 2 + a * 512);
+          vb[a][1] = *reinterpret_cast<const uint4*>(sfb + G::SFB_B / 2 + a * 512);
         }
-        const uint32_t sfa_col = tmem_base + ((uint32_t)(quarter * 32) << 16) + SF_COL0 + s * SF_STAGE_COLS;
+        const uint32_t sfa_col = tmem_base + ((uint32_t)(quarter * 32) << 16) + SF_COL0 + s * G::SF_COLS;
 #pragma unroll
         for (int a = 0; a < ATOMS; a += 2) tmem_st_x8(sfa_col + 4 * a, va[a], va[a + 1]);
 #pragma unroll
-        for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
+        for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + G::SFB_COL + 8 * a, vb[a][0], vb[a][1]);
         tmem_st_wait();
         tc_fence_before();
         if (leader && !(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
@@ -743,22 +786,23 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   if (rc != 0) return rc;
 
   // large M, unsplit: 256 x 256 tiles on CTA pairs
-  static const int use_pair = env_int("WUSH_B200_GEMM_PAIR", 0);   // measured slower than the 1-CTA kernel, see above
+  static const int use_pair = env_int("WUSH_B200_GEMM_PAIR", 1);
   if (use_pair && splits == 1 && m > 128 && sms >= 2) {
     CUtensorMap bmap2;
     rc = make_tensor_map_2d(&bmap2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
                             BK / 2, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
     auto pk = nv ? fp4_gemm_pair_kernel<true> : fp4_gemm_pair_kernel<false>;
+    const int psmem = nv ? PairGeom<true>::SMEM : PairGeom<false>::SMEM;
     static bool pair_attr_set[2] = {false, false};
     static int max_pairs[2] = {0, 0};
     if (!pair_attr_set[nv]) {
-      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem);
       if (e != cudaSuccess) return (int)e;
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * (sms / 2));
       cfg.blockDim = dim3(THREADS);
-      cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cfg.dynamicSmemBytes = psmem;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 2;
@@ -774,7 +818,7 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
     const int64_t ptiles = ((m + 255) / 256) * (int64_t)p.n_blocks;
     int64_t pairs = max_pairs[nv] < sms / 2 ? max_pairs[nv] : sms / 2;
     if (pairs > ptiles) pairs = ptiles;
-    pk<<<(unsigned)(2 * pairs), THREADS, P_SMEM_BYTES, stream>>>(amap, bmap2, p);
+    pk<<<(unsigned)(2 * pairs), THREADS, psmem, stream>>>(amap, bmap2, p);
     return (int)cudaGetLastError();
   }
 
