@@ -33,6 +33,37 @@ def test_single_gpu_update_and_overlapped():
     assert a.num_samples == b.num_samples == 3648
 
 
+def test_update_staging_matches_direct_launches():
+    """Short updates are staged and flushed by capacity, by a long input, by a dtype change and by finalize();
+    the result must equal launching on every call."""
+    from wush_b200.hessian import DistributedHessian
+    dev = torch.device("cuda:0")
+    hidden = 512
+    sizes = (300, 300, 300, 200, 2000, 17, 300)          # capacity 1000: overflow, then a long input, then a tail
+    xs = [synth.activations(t, hidden, seed=80 + i).to(dev) for i, t in enumerate(sizes)]
+    staged = DistributedHessian(hidden, dev, stage_tokens=1000)
+    direct = DistributedHessian(hidden, dev, stage_tokens=0)
+    launches = []
+    inner = staged._accumulate
+    staged._accumulate = lambda h, x, *a: (launches.append(x.shape[0]), inner(h, x, *a))[1]
+    for x in xs:
+        staged.update(x)
+        direct.update(x)
+    hs, hd = staged.finalize(), direct.finalize()
+    assert launches == [900, 200, 2000, 317]
+    assert staged.num_samples == direct.num_samples == sum(sizes)
+    assert (hs - hd).abs().max() <= 1e-6 * hd.abs().max()
+    want = wo.wush_update_sequence([synth.bf16_to_f64(x.cpu()) for x in xs])
+    assert np.abs(hs.double().cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    # fp32 inputs share the class (TF32 products): staged and direct agree to TF32 accuracy
+    f = DistributedHessian(hidden, dev)
+    for x in xs[:3]:
+        f.update(x.float())
+    hf = f.finalize().double().cpu().numpy()
+    w3 = wo.wush_update_sequence([synth.bf16_to_f64(x.cpu()) for x in xs[:3]])
+    assert np.linalg.norm(hf - w3) <= 2e-3 * np.linalg.norm(w3)
+
+
 def _worker(rank, world, port, out, peer):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist

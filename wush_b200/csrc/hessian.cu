@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
       constexpr uint32_t idesc = make_idesc_f16(F32 ? 2 /*tf32*/ : 1 /*bf16*/, 1, 1, BM, BN);
       int s = 0;
       uint32_t round = 0, it = 0;  // it counts chunks: accumulator buffer = it & 1
-      bool ok = true;
+      bool ok = true, ready = false;   // ready: the probe issued with the previous k-block saw this one complete
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         int t, kbeg, kend;
         work_range(p, w, k_blocks, t, kbeg, kend);
@@ -252,18 +252,18 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb1 = min(kb0 + CHUNK_KB, kend);
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+            if (!ready && !(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
             tc_fence_after();
             const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
-#pragma unroll
-            for (int ks = 0; ks < KT / E::KMMA; ++ks) {
-              // MN-major, 128-byte swizzle: channel atoms (128 bytes wide) are BOX_BYTES apart (leading
-              // offset), 8-token groups 1024 bytes apart (stride offset); one MMA spans KMMA tokens
-              const uint64_t ad = make_smem_desc(a0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
-              const uint64_t bd = make_smem_desc(b0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
-              if (F32) umma_tf32(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
-              else umma_f16(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
-            }
+            // MN-major, 128-byte swizzle: channel atoms (128 bytes wide) are BOX_BYTES apart (leading
+            // offset), 8- (or 4-) token groups SBO bytes apart (stride offset); one MMA spans KMMA tokens.
+            // The four MMAs of the stage go out together with a probe of the next stage's barrier.
+            static_assert(KT / E::KMMA == 4, "four MMAs per stage");
+            const uint64_t ad = make_smem_desc(a0, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+            const uint64_t bd = make_smem_desc(b0, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+            const int sn = (s + 1 == STAGES) ? 0 : s + 1;
+            ready = umma_x4_probe<F32, false>(d_tmem, ad, bd, E::KSTEP_BYTES >> 4, idesc, kb > kb0, full_bar(sn),
+                                              (sn == 0 ? round + 1 : round) & 1);
             umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
             if (++s == STAGES) { s = 0; ++round; }
           }
@@ -435,7 +435,7 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
       constexpr uint32_t idesc = make_idesc_f16(F32 ? 2 /*tf32*/ : 1 /*bf16*/, 1, 1, 256, BN);
       int s = 0;
       uint32_t round = 0, it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (int w = pair_id; w < n_work && ok; w += n_pairs) {
         int t, kbeg, kend;
         work_range(p, w, k_blocks, t, kbeg, kend);
@@ -446,16 +446,14 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int kb1 = min(kb0 + CHUNK_KB, kend);
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
+            if (!ready && !(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
             tc_fence_after();
             const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
-#pragma unroll
-            for (int ks = 0; ks < KT / E::KMMA; ++ks) {
-              const uint64_t ad = make_smem_desc(a0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
-              const uint64_t bd = make_smem_desc(b0 + ks * E::KSTEP_BYTES, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
-              if (F32) umma_tf32_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
-              else umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0) || (ks != 0));
-            }
+            const uint64_t ad = make_smem_desc(a0, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+            const uint64_t bd = make_smem_desc(b0, BOX_BYTES, E::SBO, E::DESC_SWIZZLE);
+            const int sn = (s + 1 == P_STAGES) ? 0 : s + 1;
+            ready = umma_x4_probe<F32, true>(d_tmem, ad, bd, E::KSTEP_BYTES >> 4, idesc, kb > kb0, full_bar(sn),
+                                             (sn == 0 ? round + 1 : round) & 1);
             umma_commit_pair(empty_bar(s), 3);   // frees the stage in both CTAs
             if (++s == P_STAGES) { s = 0; ++round; }
           }
@@ -492,8 +490,10 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
+          // the accumulator reads are complete (tcgen05.wait::ld) and nothing travels through memory, so the
+          // peer's arrival needs no release fence (which costs ~1600 cycles with TMA traffic in flight)
           if (leader) mbar_arrive(tempty_bar(buf));
-          else mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+          else mbar_arrive_cluster_relaxed(map_to_cta(tempty_bar(buf), 0));
         }
       }
       if (!ok) break;

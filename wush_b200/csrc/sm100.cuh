@@ -204,6 +204,42 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
       : "memory");
 }
 
+// Four MMAs (kind::f16 or kind::tf32, operand descriptors advancing by `step` descriptor units = 16 bytes) in
+// one instruction sequence, preceded by a non-blocking test of the barrier the NEXT k-block will wait on.  A
+// barrier test costs the issuing thread ~200 cycles even when the phase is complete and the MMA queue is
+// shallow, so a test between two k-blocks lets the tensor pipe run dry; here its latency overlaps the issue
+// of the MMAs and only the result is consumed afterwards.  Returns whether the probed phase is complete.
+template <bool TF32, bool PAIR>
+__device__ __forceinline__ bool umma_x4_probe(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t step, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t probe_bar, uint32_t probe_parity) {
+  uint32_t ready;
+#define WUSH_MMA4(GROUP, KIND)                                                                        \
+  asm volatile(                                                                                       \
+      "{\n.reg .pred p, q, t;\n"                                                                      \
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%12], %13;\n"                                    \
+      "setp.ne.b32 p, %11, 0;\n"                                                                      \
+      "setp.eq.b32 t, 0, 0;\n"                                                                        \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %2, %6, %10, p;\n"                       \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %3, %7, %10, t;\n"                       \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %4, %8, %10, t;\n"                       \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %5, %9, %10, t;\n"                       \
+      "selp.u32 %0, 1, 0, q;\n}\n"                                                                    \
+      : "=r"(ready)                                                                                   \
+      : "r"(d_tmem), "l"(ad), "l"(ad + step), "l"(ad + 2 * step), "l"(ad + 3 * step), "l"(bd),        \
+        "l"(bd + step), "l"(bd + 2 * step), "l"(bd + 3 * step), "r"(idesc), "r"(accumulate),          \
+        "r"(probe_bar), "r"(probe_parity)                                                             \
+      : "memory")
+  if (TF32) {
+    if (PAIR) WUSH_MMA4("2", "tf32");
+    else WUSH_MMA4("1", "tf32");
+  } else {
+    if (PAIR) WUSH_MMA4("2", "f16");
+    else WUSH_MMA4("1", "f16");
+  }
+#undef WUSH_MMA4
+  return ready != 0;
+}
+
 // ---- descriptors -------------------------------------------------------------------------------
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
 // descriptor version 1 (sm_100) and the swizzle mode in bits 61..63.

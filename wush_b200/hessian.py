@@ -48,10 +48,12 @@ def accumulate_hessian(mat_hessian: torch.Tensor, mat_input: torch.Tensor, save_
 
 def _kernel_accumulate(h: torch.Tensor, x: torch.Tensor, row_begin: int, row_end: int, lower_only: bool) -> None:
     lib = _lib.load()
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"activation dtype {x.dtype}: the kernel takes bfloat16 or float32")
+    flags = (_lib.HESSIAN_LOWER_ONLY if lower_only else 0) | (_lib.HESSIAN_INPUT_F32 if x.dtype == torch.float32 else 0)
     with torch.cuda.device(x.device):
         rc = lib.wush_hessian_accumulate_rows(h.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1], row_begin, row_end,
-                                              _lib.HESSIAN_LOWER_ONLY if lower_only else 0, None,
-                                              torch.cuda.current_stream().cuda_stream)
+                                              flags, None, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "wush_hessian_accumulate_rows")
 
 
@@ -134,7 +136,7 @@ class DistributedHessian:
     """
 
     def __init__(self, hidden: int, device, group=None, panels: int = 4, accumulate_fn=None, finalize_fn=None,
-                 peer: bool | None = None):
+                 peer: bool | None = None, stage_tokens: int | None = None):
         import os
         import torch.distributed as dist
         self.hidden, self.device, self.group, self.panels = hidden, torch.device(device), group, panels
@@ -162,6 +164,13 @@ class DistributedHessian:
         self._accumulate = accumulate_fn or _kernel_accumulate
         self._finalize = finalize_fn or _kernel_finalize
         self._comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        # update() collects short inputs (one calibration sequence per call) in a staging buffer and runs the
+        # kernel once per `stage_tokens` tokens: a 2048-token launch spends half its time on the read-modify-
+        # write of H and on partly filled waves, a 32768-token one runs at the tensor-core rate.  The buffer is
+        # capped at 1 GiB; stage_tokens=0 launches on every call.  All calls must be on one stream.
+        self._stage_cap = 32768 if stage_tokens is None else int(stage_tokens)
+        self._stage = None
+        self._staged = 0
 
     # -- per-call path (calibration hook) ----------------------------------------------------------
     def update(self, x: torch.Tensor) -> None:
@@ -169,14 +178,34 @@ class DistributedHessian:
         if not x.is_contiguous():
             x = x.contiguous()
         assert not self._reduced, "update after the cross-rank reduction"
-        self._accumulate(self.raw, x, 0, self.hidden, True)
-        self.local_tokens += x.shape[0]
+        n = x.shape[0]
+        cap = min(self._stage_cap, (1 << 30) // max(1, self.hidden * x.element_size()))
+        if n == 0:
+            return
+        if 2 * n > cap:
+            # long inputs go straight to the kernel
+            self._flush()
+            self._accumulate(self.raw, x, 0, self.hidden, True)
+        else:
+            if self._stage is not None and (self._stage.dtype != x.dtype or self._staged + n > self._stage.shape[0]):
+                self._flush()
+            if self._stage is None or self._stage.dtype != x.dtype:
+                self._stage = torch.empty(cap, self.hidden, dtype=x.dtype, device=self.device)
+            self._stage[self._staged:self._staged + n].copy_(x)
+            self._staged += n
+        self.local_tokens += n
+
+    def _flush(self) -> None:
+        if self._staged:
+            self._accumulate(self.raw, self._stage[:self._staged], 0, self.hidden, True)
+            self._staged = 0
 
     # -- all local tokens at once, reduction overlapped with compute --------------------------------
     def accumulate_overlapped(self, x: torch.Tensor) -> None:
         import torch.distributed as dist
         x = x.reshape(-1, x.shape[-1])
         assert not self._reduced
+        self._flush()
         cuda = self._comm_stream is not None
         if self.world == 1 or self._peer is not None:
             # one launch over all local tokens; with peer memory the ranks are combined in finalize()
@@ -210,6 +239,7 @@ class DistributedHessian:
     # -- result ---------------------------------------------------------------------------------------
     def finalize(self) -> torch.Tensor:
         import torch.distributed as dist
+        self._flush()
         total = self.local_tokens
         if self._peer is not None:
             pb = self._peer
