@@ -412,3 +412,101 @@ def wush_update_sequence(batches: list[np.ndarray]) -> np.ndarray:
         h += xs.T @ xs
         n += b
     return h
+
+
+# ----------------------------------------------------------------------------------
+# a12: GPTQ / Babai column sweep
+# ----------------------------------------------------------------------------------
+
+def damped_cholesky_upper(hessian: np.ndarray, damp_ratio: float = 1e-2, max_try: int = 100) -> np.ndarray:
+    """Upper Cholesky factor U (U^T U = H + damping) with the reference's retry loop,
+    src/quantization/wush_gptq.py:196-208: add damp_ratio * mean(diag) to the diagonal,
+    factor, and add the same amount again (of the already damped matrix) while it fails."""
+    h = np.array(hessian, dtype=np.float64, copy=True)
+    idx = np.arange(h.shape[-1])
+    h[idx, idx] += damp_ratio * h.diagonal().mean()
+    for _ in range(max_try):
+        try:
+            return np.linalg.cholesky(h).T.copy()
+        except np.linalg.LinAlgError:
+            h[idx, idx] += damp_ratio * h.diagonal().mean()
+    raise AssertionError("Hessian decomposition failed")
+
+
+def _solve_upper(u: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """x with u @ x = b for an upper-triangular u (back substitution, float64)."""
+    n = u.shape[0]
+    x = np.zeros_like(b, dtype=np.float64)
+    for i in range(n - 1, -1, -1):
+        x[i] = (b[i] - u[i, i + 1:] @ x[i + 1:]) / u[i, i]
+    return x
+
+
+def babai_inner(basis: np.ndarray, y: np.ndarray, fmt: str, transform: np.ndarray, force_rtn: bool) -> dict:
+    """One block of the sweep, src/quantization/wush_gptq.py:228-277, for a given block transform
+    (the reference computes it at :246 with get_transform; here the caller passes it so that a test can
+    use the very matrix another implementation chose -- 'wush' transforms are unique only up to the
+    sign convention of the SVD).
+
+    basis: (B, B) upper triangular; y: (B, R); transform: (B, B) float64 (already rounded to the model
+    dtype).  QR of basis @ transform^T (:251), rotate y (:252), solve (:254-260), quantize the rows
+    of the solution's transpose (:262); then either keep the round-to-nearest values (:264-265) or run
+    Babai's nearest-plane steps from the last coordinate to the first with the scales frozen
+    (:266-272).  Returns codes (R, B) uint8, scale bytes (R,), the dequantized transformed values
+    'fake_quant' (R, B) and 'coefficient' = transform^T @ x_transformed (B, R) (:274).
+    """
+    q, r = np.linalg.qr(basis @ transform.T)                    # :251
+    y_new = q.T @ y                                             # :252
+    x_t = _solve_upper(r, y_new)                                # :254-260
+    res = rtn_xxfp4(x_t.T, fmt)                                 # :262
+    if force_rtn:
+        x_t = res["fake_quant"].T                               # :265
+    else:
+        for i in range(r.shape[0] - 1, -1, -1):                 # :267
+            x_t[i] = y_new[i] / r[i, i]                         # :269
+            res = rtn_xxfp4(x_t.T, fmt, existing_scale=res["scale_quant"])   # :270
+            x_t = res["fake_quant"].T.copy()                    # :271
+            y_new[:i] -= r[:i, i:i + 1] * x_t[i:i + 1]          # :272
+    return {
+        "codes": res["codes"], "e2m1": res["e2m1"], "scale_quant": res["scale_quant"][..., 0],
+        "fake_quant": res["fake_quant"], "coefficient": transform.T @ x_t, "transform": transform,
+    }
+
+
+def gptq_babai_outer(weight: np.ndarray, hessian: np.ndarray | None, fmt: str, transform_type: str,
+                     force_rtn: bool, transform_fn=None) -> dict:
+    """Column sweep over blocks of one scale group, last block first,
+    src/quantization/wush_gptq.py:165-225 as quantize_layers drives it (:373-441: block size = group
+    size, force_rtn for both the outer and the inner loop, the transform rounded to the model dtype).
+
+    weight: (R, C); hessian: (C, C) or None (identity).  `transform_fn(block_index, basis, y)` overrides
+    get_transform.  Returns packed codes (R, C/2), scale bytes (R, C/G), 'fake_quant' (R, C) float64
+    (the dequantized transformed weights, :293-296), 'transform_basis' (C/G, G, G) and the sweep's
+    coefficient matrix 'x' (C, R).
+    """
+    g = FORMATS[fmt]["group"]
+    w = np.asarray(weight, dtype=np.float64)
+    n = w.shape[1]
+    x = w.T.copy()                                              # :188
+    h = np.eye(n) if hessian is None else hessian               # :191-194
+    u = damped_cholesky_upper(h)                                # :195-208
+    y = u @ x                                                   # :210
+    blocks = {}
+    for i1 in range((n - 1) // g * g, -1, -g):                  # :214
+        i2 = i1 + g
+        basis, yb = u[i1:i2, i1:i2], y[i1:i2].copy()
+        t = transform_fn(i1 // g, basis, yb) if transform_fn is not None else get_transform(basis, yb, transform_type)
+        res = babai_inner(basis, yb, fmt, t, force_rtn)         # :216-219
+        blocks[i1 // g] = res
+        if not force_rtn:
+            x[i1:i2] = res["coefficient"]                       # :221
+        y[:i1] -= u[:i1, i1:i2] @ x[i1:i2]                      # :222
+    order = sorted(blocks)
+    return {
+        "e2m1": np.concatenate([blocks[b]["e2m1"] for b in order], axis=-1),
+        "codes": np.concatenate([blocks[b]["codes"] for b in order], axis=-1),
+        "scale_quant": np.stack([blocks[b]["scale_quant"] for b in order], axis=-1),
+        "fake_quant": np.concatenate([blocks[b]["fake_quant"] for b in order], axis=-1),
+        "transform_basis": np.stack([blocks[b]["transform"] for b in order]),
+        "x": x,
+    }

@@ -2,7 +2,8 @@
 
 Usage (needs the reference checkout; writes next to this file):
 
-    python tests/golden/make_golden.py /path/to/WUSH
+    python tests/golden/make_golden.py /path/to/WUSH          # reference_vectors.npz
+    python tests/golden/make_golden.py /path/to/WUSH sweep    # sweep_vectors.npz (column sweep)
 
 The reference has no numeric tests or fixtures of its own, so these files -- outputs of
 its pure-torch quantizer (src/quantization/wush_gptq.py) on small seeded inputs and
@@ -153,5 +154,50 @@ def main(root: str) -> None:
     print("wrote", os.path.join(HERE, "reference_vectors.npz"), {k: v.shape for k, v in out.items()})
 
 
+def sweep_vectors(root: str) -> None:
+    """Column sweep (gptq_babai_outer driven as quantize_layers drives it, wush_gptq.py:373-441) on
+    small layers, both formats, three transforms, round-to-nearest and GPTQ, written to
+    sweep_vectors.npz.  collate_xxfp4 cannot run on CPU (torch.cat of float4 tensors), so the blocks
+    are collated here through uint8 views; everything else is the reference's code."""
+    import functools
+    ref = _import_reference(root)
+    g = torch.Generator().manual_seed(4321)
+    out: dict[str, np.ndarray] = {}
+    for fmt, grp in (("mxfp4", 32), ("nvfp4", 16)):
+        c, r, tok = 4 * grp, 40, 3 * grp
+        xc = torch.randn(tok, c, generator=g, dtype=torch.float64)
+        xc[:, 5] *= 50.0
+        h = (xc.T @ xc / tok).to(torch.float32)
+        w = (torch.randn(r, c, generator=g) * 0.02).to(torch.bfloat16)
+        out[f"{fmt}_w"], out[f"{fmt}_h"] = w.to(torch.float64).numpy(), h.to(torch.float64).numpy()
+        kw = dict(mxfp4=dict(group_size=32, scale_dtype=torch.float8_e8m0fnu, scale_scale=4., global_scale=3.),
+                  nvfp4=dict(group_size=16, scale_dtype=torch.float8_e4m3fn, scale_scale=6., global_scale=10.))[fmt]
+        quant_fn = functools.partial(ref.rtn_xxfp4, fp4_rounding_mode="even", **kw)
+        for tt in ("identity", "hadamard", "wush"):
+            for rtn in (True, False):
+                collate = lambda *results, **_: results
+                res = ref.gptq_babai_outer(
+                    parameter=w, hessian=h,
+                    inner_fn=functools.partial(
+                        ref.block_transform_gptq_babai_inner, quant_fn=quant_fn,
+                        basis_transform_fn=functools.partial(ref.get_transform, transform_type=tt,
+                                                             transform_dtype=torch.bfloat16),
+                        force_rtn_inner=rtn),
+                    collate_fn=collate, block_size=grp, force_rtn_outer=rtn)
+                tag = f"{fmt}_{tt}_{'rtn' if rtn else 'gptq'}"
+                out[tag + "_e2m1"] = np.concatenate([_u8(x["e2m1"]) for x in res], axis=-1)
+                out[tag + "_scale"] = np.concatenate([_u8(x["scale_quant"]) for x in res], axis=-1)
+                out[tag + "_fake"] = torch.cat([ref.dequant_xxfp4(x["e2m1"], x["scale_quant"], x["global_scale"],
+                                                                  dtype=torch.float64) for x in res], dim=-1).numpy()
+                out[tag + "_transform"] = torch.stack([x["transform_basis"].to(torch.bfloat16).to(torch.float64)
+                                                       for x in res]).numpy()
+    np.savez_compressed(os.path.join(HERE, "sweep_vectors.npz"), **out)
+    print("wrote", os.path.join(HERE, "sweep_vectors.npz"), {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) > 2 and sys.argv[2] == "sweep":
+        sweep_vectors(root)
+    else:
+        main(root)
