@@ -221,6 +221,37 @@ WUSH_API int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b, 
 /* Scratch bytes the automatic split-K choice would use for this problem on the current device (0 = none). */
 WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
+/*
+ * One block of the GPTQ / Babai column sweep, all weight rows at once.
+ *
+ * Replaces the part of block_transform_gptq_babai_inner after its QR factorization
+ * (src/quantization/wush_gptq.py:254-274): the triangular solve for the transformed coefficients, the
+ * quantizer call rtn_xxfp4 (:91-138, constants of :388-407), the nearest-plane loop that re-quantizes with
+ * frozen scales and updates the remaining targets (:266-272), and the coefficient product transform^T . x
+ * (:274); it also writes what collate_xxfp4 (:280-301) assembles.  With nblocks > 1 it handles independent
+ * blocks in one launch (round-to-nearest mode, where no block depends on another).
+ *
+ *   rn       float64 [nblocks, G, G]   upper-triangular factor of basis . transform^T
+ *   ynew     float64 [nblocks, G, rows] rotated targets Q^T y
+ *   tmat     float64 [nblocks, G, G]   block transforms (already rounded to the model dtype)
+ *   codes    u8 [rows, cols/2]  packed E2M1 (element 2i in the low nibble); this call writes columns
+ *            [(col_block0 + b) * G/2, +G/2) of every row for b < nblocks
+ *   scales   u8 [rows, cols/G]  E8M0 / E4M3 bytes, column col_block0 + b
+ *   fake     bf16 (or fp32 with WUSH_SWEEP_FAKE_F32) [rows, cols] dequantized transformed weights, or NULL
+ *   coef     float64 [nblocks, G, rows] transform^T . x_quantized, or NULL
+ *   format   WUSH_FORMAT_MXFP4 (G = 32, E8M0 scales) / WUSH_FORMAT_NVFP4 (G = 16, E4M3, tensor scale 10)
+ *   flags    WUSH_SWEEP_RTN_ONLY: round to nearest only (force_rtn), no nearest-plane loop
+ * Float64 arithmetic in the reference's operation order; ties round to the even code; exact zeros encode
+ * as -0 like the reference's quantizer does.
+ */
+#define WUSH_FORMAT_MXFP4 0
+#define WUSH_FORMAT_NVFP4 1
+#define WUSH_SWEEP_RTN_ONLY 1
+#define WUSH_SWEEP_FAKE_F32 2
+WUSH_API int wush_gptq_block_step(const double* rn, const double* ynew, const double* tmat, int nblocks,
+                                  int col_block0, int64_t rows, int64_t cols, int format, int flags, uint8_t* codes,
+                                  uint8_t* scales, void* fake, double* coef, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
