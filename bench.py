@@ -11,7 +11,8 @@ the activations and D2H of codes+scales inside the timed region).  `roofline` co
 kernel, `cpu_baseline` times the CPU restatement of the reference's torch quantizer on a bounded
 sample.  `extra.gemm` (MXFP4 GEMM at 8192^3, TFLOP/s) and `extra.hessian` (262144 calibration tokens
 at hidden 4096, sharded over the GPUs with an NCCL all-reduce, tok/s) carry the other two kernels of
-the path with their own roofline and CPU-baseline objects.
+the path with their own roofline and CPU-baseline objects; `extra.sweep` times the GPTQ column sweep of one
+4096 x 4096 layer.
 
 With --impl reference the reference's CPU path (the oracle port; the reference is pure Python
 and needs its own checkout to import) is timed on the host cores for the same workload.
@@ -209,10 +210,62 @@ def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
     return {"metric": "mxfp4_w4a4_gemm_TFLOPS", "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms,
             "config": {"workload": f"MXFP4 GEMM M=N=K={GEMM_M}, bf16 out, operands from the fused quantize kernel"},
             "gpu_launches": args.steps,
-            "roofline": {"bound": "tensor", "kernel": "fp4_gemm_kernel<MX>", "achieved": tflops, "peak": peak4,
+            "roofline": {"bound": "tensor", "kernel": "fp4_gemm_pair_kernel<MX>", "achieved": tflops, "peak": peak4,
                          "unit": "TFLOP/s", "frac": tflops / peak4,
                          "peak_kind": f"4 x {peak_kind} bf16 burst (no FP4 figure was measured)",
                          "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None}}
+
+
+SWEEP_ROWS, SWEEP_COLS, SWEEP_CALIB = 4096, 4096, 32768
+
+
+def bench_sweep(args, dev, torch) -> dict:
+    """Column sweep of one 4096 x 4096 layer (MXFP4, WUSH transforms, second moment from 16 x 2048 synthetic
+    calibration tokens): round-to-nearest (all blocks in one kernel launch) and GPTQ (block after block).
+    Every rank sweeps its own layer: layers are independent, there is no collective."""
+    from oracle import synth
+    from wush_b200 import gptq
+    from wush_b200.hessian import accumulate_hessian
+    x = synth.activations(SWEEP_CALIB, SWEEP_COLS, seed=400).to(dev)
+    h = accumulate_hessian(torch.zeros(SWEEP_COLS, SWEEP_COLS, device=dev), x)
+    h /= SWEEP_CALIB
+    del x
+    w = synth.weights(SWEEP_ROWS, SWEEP_COLS, seed=401).to(dev)
+    out = {}
+    for name, rtn, reps in (("rtn", True, 3), ("gptq", False, 1)):
+        gptq.gptq_babai_sweep(w, h, "mxfp4", "wush", force_rtn=rtn)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            gptq.gptq_babai_sweep(w, h, "mxfp4", "wush", force_rtn=rtn)
+        torch.cuda.synchronize()
+        out[name + "_ms_per_layer"] = (time.perf_counter() - t0) * 1e3 / reps
+    nb = SWEEP_COLS // 32
+    return {"metric": "column_sweep_weight_rows_per_s", "value": SWEEP_ROWS / (out["rtn_ms_per_layer"] * 1e-3),
+            "unit": "rows/s", **out,
+            "config": {"workload": f"W {SWEEP_ROWS}x{SWEEP_COLS} bf16 N(0,0.02^2), MXFP4, WUSH transforms, H from "
+                                   f"{SWEEP_CALIB} synthetic tokens; host wall clock incl. Cholesky and all torch ops"},
+            "gpu_launches": 4 * (1 + nb), "note": "value is the round-to-nearest sweep; gptq_ms_per_layer is the "
+            "sequential nearest-plane sweep (one wush_gptq_block_step launch per 32-column block)"}
+
+
+def cpu_sweep_throughput() -> dict:
+    """The oracle's restatement of gptq_babai_outer (round-to-nearest, WUSH transforms) on a bounded sample:
+    all 4096 input channels, 256 of the 4096 weight rows (rows are independent; the Cholesky factorization
+    of H is a fixed cost paid in both arms)."""
+    import numpy as np
+    from oracle import synth
+    from oracle import wush_oracle as wo
+    rows = 256
+    x = synth.bf16_to_f64(synth.activations(4096, SWEEP_COLS, seed=400))
+    h = x.T @ x / x.shape[0]
+    w = synth.bf16_to_f64(synth.weights(rows, SWEEP_COLS, seed=401))
+    t0 = time.perf_counter()
+    wo.gptq_babai_outer(w, h, "mxfp4", "wush", True)
+    sec = time.perf_counter() - t0
+    return {"value": rows / sec, "unit": "rows/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"{rows} of {SWEEP_ROWS} weight rows, all {SWEEP_COLS} channels, round-to-nearest sweep in "
+                      f"NumPy float64 (BLAS threads as configured): {sec:.2f} s"}
 
 
 def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=HESS_HIDDEN) -> dict:
@@ -390,7 +443,7 @@ def run_ours(args) -> None:
         gemm = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
         hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
         hess_ffn = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
-        extra = {"gemm": gemm, "hessian": hess, "hessian_hidden14336": hess_ffn}
+        extra = {"gemm": gemm, "hessian": hess, "hessian_hidden14336": hess_ffn, "sweep": bench_sweep(args, dev, torch)}
 
     if rank == 0:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9
@@ -402,6 +455,7 @@ def run_ours(args) -> None:
             cpu.pop("seconds", None)
             extra["gemm"]["cpu_baseline"] = cpu_gemm_throughput()
             extra["hessian"]["cpu_baseline"] = cpu_hessian_throughput()
+            extra["sweep"]["cpu_baseline"] = cpu_sweep_throughput()
         launches = args.steps + sum(v.get("gpu_launches", 0) for v in extra.values())
         line = {
             "metric": "fused_transform_quant_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
