@@ -170,3 +170,28 @@ def test_full_size_properties():
     ref = wo.fused_transform_quant(synth.bf16_to_f64(x[sample].cpu()), wm.cpu().to(torch.float64).numpy(), "mxfp4")
     assert mismatch_fraction(canon_codes(np_u8(q1[sample])), canon_codes(ref["e2m1"])) <= TIE_BUDGET
     assert mismatch_fraction(np_u8(s1)[sample.cpu().numpy()][:, : cols // 32], ref["scale_quant"]) <= TIE_BUDGET
+
+
+def test_host_streamed_quantize_matches_single_launch():
+    """Row-chunked, three-stream pass over pinned host buffers == one launch on the device (rows are
+    independent), for a row count that is not a multiple of the chunk."""
+    from wush_b200 import qutlass_ops as ops
+    from wush_b200.host_stream import HostQuantizer
+    dev = torch.device("cuda:0")
+    rows, cols = 5 * 256 + 77, 1024
+    x = synth.activations(rows, cols, seed=123)
+    for fmt, g in (("mx", 32), ("nv", 16)):
+        mat = synth.to_bf16_tensor(synth.wush_matrix(cols, g, seed=7)).to(dev)
+        gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+        q_ref, sf_ref = ops._quantize(x.to(dev), mat, fmt, gs)
+        xh = x.pin_memory()
+        qh = torch.empty(rows, cols // 2, dtype=torch.uint8).pin_memory()
+        sh = torch.empty(rows, cols // g, dtype=torch.uint8).pin_memory()
+        hq = HostQuantizer(cols, mat, fmt, gs, chunk_rows=256)
+        for _ in range(2):                      # second pass reuses the staging buffers
+            qh.zero_(); sh.zero_()
+            hq(xh, qh, sh)
+            hq.synchronize()
+            assert torch.equal(qh, q_ref.cpu())
+            assert torch.equal(sh, sf_ref.view(torch.uint8)[:rows, : cols // g].cpu())
+        assert hq.launches == 2 * 6
