@@ -195,3 +195,27 @@ def test_host_streamed_quantize_matches_single_launch():
             assert torch.equal(qh, q_ref.cpu())
             assert torch.equal(sh, sf_ref.view(torch.uint8)[:rows, : cols // g].cpu())
         assert hq.launches == 2 * 6
+
+
+def test_pseudo_quant_wrappers_match_oracle_dequantization():
+    """The Triton-wrapper-compatible entry points return dequant(quant(x @ H)) of the oracle."""
+    from wush_b200 import pseudo_quant as pq
+    dev = torch.device("cuda:0")
+    x = synth.activations(96, 512, seed=321)
+    for fmt, g in (("mxfp4", 32), ("nvfp4", 16)):
+        hm = synth.to_bf16_tensor(synth.hadamard_matrix(g))
+        want = wo.fused_transform_quant(synth.bf16_to_f64(x), synth.bf16_to_f64(hm), fmt)["fake_quant"]
+        hm = hm.to(dev)
+        if fmt == "mxfp4":
+            got, mask = pq.mxfp4_forward_kernel_wrapper(x.to(dev).reshape(2, 48, 512), hm, return_clip_mask=True, quest=False)
+            assert mask.dtype == torch.bool and bool(mask.all()) and mask.shape == got.shape
+            with pytest.raises(NotImplementedError):
+                pq.mxfp4_forward_kernel_wrapper(x.to(dev), hm)          # quest=True is the reference's default
+        else:
+            got = pq.nvfp4_forward_kernel_wrapper(x.to(dev).reshape(2, 48, 512), hm, torch.tensor(10.0, device=dev))
+        assert got.shape == (2, 48, 512) and got.dtype == torch.bfloat16
+        want_bf16 = torch.from_numpy(want).to(torch.bfloat16).float().numpy().reshape(2, 48, 512)
+        bad = np.mean(got.float().cpu().numpy() != want_bf16)
+        assert bad <= 1e-4, bad
+    y = pq.pseudoquantize_fp(x.to(dev), "mxfp4")
+    assert y.shape == x.shape

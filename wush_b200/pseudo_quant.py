@@ -1,0 +1,58 @@
+"""Pseudo-quantization (quantize, then dequantize) with the call signatures of the reference's Triton wrappers
+``mxfp4_forward_kernel_wrapper`` (inference_lib/src/fp_quant/module/triton/mxfp4.py:136-176) and
+``nvfp4_forward_kernel_wrapper`` (.../triton/nvfp4.py:122-149), and ``pseudoquantize_fp``
+(src/utils/wush_utils.py:6-53) on top of them.  The fused transform + quantize kernel produces codes and
+scales; the values are rebuilt from them.
+
+Differences from the Triton kernels: ties round to the even code (the reference's torch quantizer's rule; the
+Triton kernels round ties toward zero), and only the abs-max scaling the WUSH pipeline uses is implemented
+(``quest=False``, ``gaussian_scale=3/4``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import qutlass_ops as ops
+from .gptq import dequantize
+
+
+def _flat(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+
+
+def mxfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor, return_clip_mask: bool = False,
+                                 gaussian_scale: float = 3 / 4, quest: bool = True):
+    """(dequantized tensor like x, clip mask | None).  x @ hadamard_matrix per 32-element group, E8M0 abs-max
+    scale, E2M1 values.  The abs-max scale never clips, so the mask is all True."""
+    if quest or abs(gaussian_scale - 0.75) > 1e-12:
+        raise NotImplementedError("only quest=False with gaussian_scale=3/4 (abs-max scaling) is implemented")
+    if hadamard_matrix.shape[-1] != 32:
+        raise NotImplementedError("the transform must be 32 x 32 (one scale group)")
+    xf = _flat(x)
+    q, sf = ops._quantize(xf, hadamard_matrix.to(device=x.device, dtype=torch.bfloat16), "mx", None)
+    out = dequantize(q, sf[: xf.shape[0], : xf.shape[1] // 32], "mxfp4").to(x.dtype).reshape(x.shape)
+    return out, (torch.ones_like(x, dtype=torch.bool) if return_clip_mask else None)
+
+
+def nvfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor) -> torch.Tensor:
+    """Dequantized tensor like x: x @ hadamard_matrix per 16-element group, E4M3 scale of absmax * global_scale / 6,
+    E2M1 values, divided by global_scale again."""
+    if hadamard_matrix.shape[-1] != 16:
+        raise NotImplementedError("the transform must be 16 x 16 (one scale group)")
+    xf = _flat(x)
+    gs = global_scale.to(device=x.device, dtype=torch.float32).reshape(-1)[:1]
+    q, sf = ops._quantize(xf, hadamard_matrix.to(device=x.device, dtype=torch.bfloat16), "nv", gs)
+    lut_vals = dequantize(q, sf[: xf.shape[0], : xf.shape[1] // 16], "nvfp4") * (10.0 / gs)   # dequantize() divides by 10
+    return lut_vals.to(x.dtype).reshape(x.shape)
+
+
+def pseudoquantize_fp(x: torch.Tensor, dtype: str) -> torch.Tensor:
+    """src/utils/wush_utils.py:6-53: identity transform, abs-max scaling."""
+    if dtype == "mxfp4":
+        return mxfp4_forward_kernel_wrapper(x, torch.eye(32, dtype=x.dtype, device=x.device), return_clip_mask=True,
+                                            quest=False, gaussian_scale=3.0 / 4.0)[0]
+    if dtype == "nvfp4":
+        return nvfp4_forward_kernel_wrapper(x, torch.eye(16, dtype=x.dtype, device=x.device),
+                                            torch.as_tensor(10.0, dtype=x.dtype, device=x.device))
+    raise ValueError(f"Unsupported forward dtype: {dtype}")
