@@ -232,7 +232,8 @@ WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
  * blocks in one launch (round-to-nearest mode, where no block depends on another).
  *
  *   rn       float64 [nblocks, G, G]   upper-triangular factor of basis . transform^T
- *   ynew     float64 [nblocks, G, rows] rotated targets Q^T y
+ *   ynew     float64 [nblocks, G, rows] rotated targets Q^T y -- or the raw targets y when qt is given
+ *   qt       float64 [nblocks, G, G]   Q^T; the kernel then rotates the targets itself (:252).  NULL: ynew is rotated
  *   tmat     float64 [nblocks, G, G]   block transforms (already rounded to the model dtype)
  *   codes    u8 [rows, cols/2]  packed E2M1 (element 2i in the low nibble); this call writes columns
  *            [(col_block0 + b) * G/2, +G/2) of every row for b < nblocks
@@ -248,9 +249,39 @@ WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 #define WUSH_FORMAT_NVFP4 1
 #define WUSH_SWEEP_RTN_ONLY 1
 #define WUSH_SWEEP_FAKE_F32 2
-WUSH_API int wush_gptq_block_step(const double* rn, const double* ynew, const double* tmat, int nblocks,
-                                  int col_block0, int64_t rows, int64_t cols, int format, int flags, uint8_t* codes,
-                                  uint8_t* scales, void* fake, double* coef, void* stream);
+WUSH_API int wush_gptq_block_step(const double* rn, const double* ynew, const double* qt, const double* tmat,
+                                  int nblocks, int col_block0, int64_t rows, int64_t cols, int format, int flags,
+                                  uint8_t* codes, uint8_t* scales, void* fake, double* coef, void* stream);
+
+/*
+ * The G x G dense algebra of one sweep block (or of nblocks independent blocks), one CTA per block.
+ *
+ * Replaces get_transform (src/quantization/wush_gptq.py:304-347) and the QR factorization at the top of
+ * block_transform_gptq_babai_inner (:251-252):
+ *   'wush': V, s = left singular vectors / values of the block's targets y, taken from the eigen-decomposition
+ *   of gram = y y^T (cyclic Jacobi); s *= rows^-1/2; s += 1 % of mean(s); T = Had diag(s^1/2) V^T basis^-T
+ *   (:331-341; 'wus': identity instead of the Hadamard matrix); T is rounded to the model dtype (:345);
+ *   then Q R = basis T^T by Householder reflections.
+ * The sign of every singular vector is fixed by making its largest component positive (an SVD leaves it open).
+ *
+ *   gram        float64 [nblocks, G, G] (read for WUSH / WUS only)
+ *   basis       float64 G x G upper-triangular diagonal block of the Cholesky factor, row stride ldb; block b
+ *               starts basis_step * b elements further (G * ldb + G walks down the diagonal of one factor)
+ *   transform   WUSH_TRANSFORM_*; GIVEN reads tmat instead of computing it
+ *   flags       WUSH_SWEEP_FAKE_F32: the model dtype is fp32 (round T to fp32 instead of bf16)
+ *   rows        number of weight rows R (for the R^-1/2 factor)
+ *   tmat, rn, qt  float64 [nblocks, G, G] out: transform, R (upper triangular), Q^T -- the inputs of
+ *               wush_gptq_block_step (which rotates the raw targets itself when given qt)
+ *   status      optional DEVICE int, set to 1 if a transform is not finite
+ */
+#define WUSH_TRANSFORM_IDENTITY 0
+#define WUSH_TRANSFORM_HADAMARD 1
+#define WUSH_TRANSFORM_WUSH 2
+#define WUSH_TRANSFORM_WUS 3
+#define WUSH_TRANSFORM_GIVEN 4
+WUSH_API int wush_gptq_block_prepare(const double* gram, const double* basis, int64_t ldb, int64_t basis_step,
+                                     int nblocks, int format, int transform, int flags, int64_t rows, double* tmat,
+                                     double* rn, double* qt, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,6 +25,7 @@ HESSIAN_LOWER_ONLY = 1
 HESSIAN_INPUT_F32 = 2
 FORMAT_MXFP4, FORMAT_NVFP4 = 0, 1
 SWEEP_RTN_ONLY, SWEEP_FAKE_F32 = 1, 2
+TRANSFORMS = {"identity": 0, "hadamard": 1, "wush": 2, "wus": 3, "given": 4}
 
 _lib = None
 
@@ -64,7 +65,8 @@ def load() -> ctypes.CDLL:
         "wush_hessian_peer_reduce": [vp, vp, i32, i32, i64, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
-        "wush_gptq_block_step": [vp, vp, vp, i32, i32, i64, i64, i32, i32, vp, vp, vp, vp, vp],
+        "wush_gptq_block_step": [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, vp, vp, vp, vp, vp],
+        "wush_gptq_block_prepare": [vp, vp, i64, i64, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)

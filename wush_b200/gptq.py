@@ -2,15 +2,15 @@
 ``quantize_layers`` / ``gptq_babai_outer`` / ``block_transform_gptq_babai_inner`` / ``get_transform`` /
 ``collate_xxfp4`` of the reference (src/quantization/wush_gptq.py:165-441).
 
-Division of labour.  The dense float64 linear algebra the reference does with torch stays with torch on the
-GPU (cuSOLVER / cuBLAS: damped Cholesky of the Hessian, the per-block symmetric eigenproblem and QR, the
-trailing update of the targets).  Everything per weight row -- triangular solve, scale choice, E2M1
-rounding, the nearest-plane loop with frozen scales, the coefficient product and the packing the
-reference does in ``collate_xxfp4`` -- is one launch of ``wush_gptq_block_step`` per block.
+Division of labour.  The large float64 matrices stay with cuSOLVER / cuBLAS through torch (damped Cholesky of the
+Hessian, the Gram matrix of a block's targets, the update of the remaining targets).  The 32 x 32 algebra of a
+block -- eigen-decomposition, WUSH transform, rounding, QR -- is one CTA (``wush_gptq_block_prepare``), and
+everything per weight row -- rotation, triangular solve, scale choice, E2M1 rounding, the nearest-plane loop with
+frozen scales, the coefficient product and the packing the reference does in ``collate_xxfp4`` -- is one launch
+of ``wush_gptq_block_step``.
 
-Round-to-nearest mode (``force_rtn=True``) has no dependency between blocks, so all blocks are factored in
-batched calls and quantized by ONE kernel launch.  GPTQ mode walks the blocks from last to first like the
-reference.
+Round-to-nearest mode (``force_rtn=True``) has no dependency between blocks, so all blocks are handled by one
+launch of each kernel.  GPTQ mode walks the blocks from last to first like the reference.
 
 Differences from the reference, both inside its own numerical freedom:
 * the singular vectors of the block targets come from the eigen-decomposition of the G x G Gram matrix
@@ -51,7 +51,7 @@ def damped_cholesky_upper(hessian: torch.Tensor, damp_ratio: float = 1e-2, max_t
     for _ in range(max_try):
         u, info = torch.linalg.cholesky_ex(h, upper=True, check_errors=False)
         if not bool(info.any()):
-            return u
+            return u.contiguous()      # the kernels index it row-major (cholesky_ex may return a transposed view)
         d += damp_ratio * d.mean()
     raise AssertionError("Hessian decomposition failed. Please try using more samples or increasing damp_ratio.")
 
@@ -89,17 +89,23 @@ def get_transform(basis: torch.Tensor, y: torch.Tensor, transform_type: str = "i
     return t
 
 
-def _block_step(rn, ynew, tmat, col_block0, codes, scales, fake, coef, fmt, rtn):
+def _prepare(gram, basis, ldb, basis_step, nblocks, fmt, transform, fake_f32, rows, tmat, rn, qt, status):
     lib = _lib.load()
-    nblocks, g, rows = ynew.shape
-    flags = (_lib.SWEEP_RTN_ONLY if rtn else 0) | (_lib.SWEEP_FAKE_F32 if fake is not None and fake.dtype == torch.float32 else 0)
-    for t in (rn, ynew, tmat):
-        assert t.is_contiguous() and t.dtype == torch.float64
-    with torch.cuda.device(ynew.device):
-        rc = lib.wush_gptq_block_step(rn.data_ptr(), ynew.data_ptr(), tmat.data_ptr(), nblocks, col_block0, rows,
-                                      codes.shape[1] * 2, fmt, flags, codes.data_ptr(), scales.data_ptr(),
-                                      fake.data_ptr() if fake is not None else None,
-                                      coef.data_ptr() if coef is not None else None,
+    with torch.cuda.device(tmat.device):
+        rc = lib.wush_gptq_block_prepare(gram.data_ptr() if gram is not None else None, basis.data_ptr(), ldb, basis_step,
+                                         nblocks, fmt, _lib.TRANSFORMS[transform], _lib.SWEEP_FAKE_F32 if fake_f32 else 0,
+                                         rows, tmat.data_ptr(), rn.data_ptr(), qt.data_ptr(), status.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "wush_gptq_block_prepare")
+
+
+def _block_step(rn, y, qt, tmat, nblocks, col_block0, rows, codes, scales, fake, coef, fmt, rtn):
+    lib = _lib.load()
+    flags = (_lib.SWEEP_RTN_ONLY if rtn else 0) | (_lib.SWEEP_FAKE_F32 if fake.dtype == torch.float32 else 0)
+    with torch.cuda.device(codes.device):
+        rc = lib.wush_gptq_block_step(rn.data_ptr(), y.data_ptr(), qt.data_ptr(), tmat.data_ptr(), nblocks, col_block0,
+                                      rows, codes.shape[1] * 2, fmt, flags, codes.data_ptr(), scales.data_ptr(),
+                                      fake.data_ptr(), coef.data_ptr() if coef is not None else None,
                                       torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "wush_gptq_block_step")
 
@@ -115,17 +121,24 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
     ((C/G, G, G), optional) overrides the computed block transforms.  Returns a dict with
     'fake_quant' (R, C) weight dtype, 'qweight' (R, C/2) uint8 packed E2M1, 'scale_quant' (R, C/G) float8,
     'transform_basis' (C/G, G, G) weight dtype and 'global_scale'.
+
+    Per block the GPU runs: the Gram matrix of the targets (cuBLAS), `wush_gptq_block_prepare` (transform, QR),
+    `wush_gptq_block_step` (everything per weight row) and the update of the remaining targets (cuBLAS) --
+    four launches and no host synchronisation; round-to-nearest mode does all blocks with one launch of each.
     """
     if not weight.is_cuda:
         raise RuntimeError("wush_b200 runs on CUDA devices only")
     if weight.dtype not in (torch.bfloat16, torch.float32):
         raise NotImplementedError(f"weight dtype {weight.dtype}")
+    if transform_class not in ("identity", "hadamard", "wush", "wus"):
+        raise NotImplementedError(transform_class)
     f = _FORMATS[quant_type]
     g, fmt = f["group"], f["fmt"]
     rows, cols = weight.shape
     if cols % g:
         raise ValueError(f"in_features must be a multiple of {g}")
     dev, nb = weight.device, cols // g
+    f32 = weight.dtype == torch.float32
     x = weight.t().to(torch.float64).contiguous()                                     # (C, R), :188
     h = torch.eye(cols, dtype=torch.float64, device=dev) if hessian is None else hessian.to(dev)
     u = damped_cholesky_upper(h)                                                      # :195-208
@@ -134,37 +147,41 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
     scales = torch.empty(rows, nb, dtype=torch.uint8, device=dev)
     fake = torch.empty(rows, cols, dtype=weight.dtype, device=dev)
     tb = torch.empty(nb, g, g, dtype=torch.float64, device=dev)
-
-    def factor(basis, yb, t):
-        # QR of basis . T^T (:251); only R and Q^T y are needed (:252)
-        q, rn = torch.linalg.qr(basis @ t.transpose(-2, -1), mode="reduced")
-        return rn.contiguous(), (q.transpose(-2, -1) @ yb).contiguous()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    transform = transform_class
+    if transforms is not None:
+        tb.copy_(transforms.to(torch.float64))
+        transform = "given"
+    need_gram = transform in ("wush", "wus")
+    diag_step = g * cols + g                      # from one diagonal block of u to the next
 
     if force_rtn:
         # no error feedback between blocks: the targets of block b are U_bb x_b (what :210-222 leave in y
-        # when x is never updated), and every block can be factored and quantized at once
+        # when x is never updated), and every block is prepared and quantized at once
         idx = torch.arange(nb, device=dev)
-        ur = u.view(nb, g, nb, g)
-        basis = ur[idx, :, idx, :].contiguous()                                       # (nb, G, G) diagonal blocks
+        basis = u.view(nb, g, nb, g)[idx, :, idx, :].contiguous()                     # (nb, G, G) diagonal blocks
         yb = basis @ x.view(nb, g, rows)
-        t = transforms.to(torch.float64) if transforms is not None else get_transform(basis, yb, transform_class, weight.dtype)
-        rn, ynew = factor(basis, yb, t)
-        tb.copy_(t)
-        _block_step(rn, ynew, tb, 0, codes, scales, fake, None, fmt, True)
+        gram = yb @ yb.transpose(-2, -1) if need_gram else None
+        rn, qt = torch.empty_like(tb), torch.empty_like(tb)
+        _prepare(gram, basis, g, g * g, nb, fmt, transform, f32, rows, tb, rn, qt, status)
+        _block_step(rn, yb, qt, tb, nb, 0, rows, codes, scales, fake, None, fmt, True)
     else:
         y = u @ x                                                                     # :210
-        coef = torch.empty(1, g, rows, dtype=torch.float64, device=dev)
+        rn = torch.empty(g, g, dtype=torch.float64, device=dev)
+        qt = torch.empty_like(rn)
+        gram = torch.empty_like(rn) if need_gram else None
         for b in range(nb - 1, -1, -1):                                               # :214
             i1, i2 = b * g, (b + 1) * g
-            basis, yb = u[i1:i2, i1:i2], y[i1:i2]
-            t = (transforms[b].to(torch.float64) if transforms is not None
-                 else get_transform(basis, yb, transform_class, weight.dtype))
-            rn, ynew = factor(basis, yb, t)
-            tb[b] = t
-            _block_step(rn[None], ynew[None], tb[b:b + 1], b, codes, scales, fake, coef, fmt, False)
-            x[i1:i2] = coef[0]                                                        # :221
+            yb = y[i1:i2]
+            if need_gram:
+                torch.mm(yb, yb.t(), out=gram)
+            _prepare(gram, u[i1:i2, i1:i2], cols, diag_step, 1, fmt, transform, f32, rows, tb[b], rn, qt, status)
+            # the coefficients go straight into x (:221), which the update of the remaining targets reads (:222)
+            _block_step(rn, yb, qt, tb[b], 1, b, rows, codes, scales, fake, x[i1:i2], fmt, False)
             if i1:
-                y[:i1].addmm_(u[:i1, i1:i2], coef[0], alpha=-1.0)                     # :222
+                y[:i1].addmm_(u[:i1, i1:i2], x[i1:i2], alpha=-1.0)
+    if int(status.item()):
+        raise AssertionError("non-finite block transform")
     return {
         "fake_quant": fake,
         "qweight": codes,
