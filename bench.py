@@ -216,6 +216,57 @@ def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
                          "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None}}
 
 
+SHARD_M, SHARD_N, SHARD_K = 32768, 8192, 8192      # 16 x 2048 tokens through one hidden-8192 projection
+
+
+def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
+    """MXFP4 linear layer with the weight rows sharded over the ranks (70B-shape projection: 32768 tokens,
+    8192 -> 8192): GEMM with the peer-store epilogue (the all-gather of the output columns happens inside the
+    kernel) next to the local GEMM + NCCL all-gather baseline.  Activations are replicated."""
+    from oracle import synth
+    from wush_b200 import _lib
+    from wush_b200 import qutlass_ops as ops
+    from wush_b200.sharded import ColumnShardedFP4Linear, shard_bounds
+    rank = dist.get_rank() if world > 1 else 0
+    g = torch.Generator(device=dev).manual_seed(11)
+    had = synth.to_bf16_tensor(synth.hadamard_matrix(32)).to(dev)
+    x = torch.randn(SHARD_M, SHARD_K, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    xq, xs = ops._quantize(x, had, "mx", None, sf_layout=_lib.SF_BLOCKED)
+    del x
+    c0, c1 = shard_bounds(SHARD_N, world, rank)
+    w = (torch.randn(c1 - c0, SHARD_K, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wq, wsf = ops._quantize(w, had, "mx", None)
+    del w
+    res = {}
+    for name, peer in (("fused", True), ("nccl", False)):
+        layer = ColumnShardedFP4Linear(wq, wsf[: c1 - c0, : SHARD_K // 32], SHARD_N, "mx", 1.0 / 9.0, max_tokens=SHARD_M,
+                                       peer=peer)
+        for _ in range(3):
+            layer.forward(xq, xs.view(-1))
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            layer.forward(xq, xs.view(-1))
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name + "_ms"] = float(t.item())
+        res[name + "_path"] = "peer-store epilogue" if layer.fused else ("NCCL all-gather" if world > 1 else "local")
+        del layer
+    flops = 2.0 * SHARD_M * SHARD_N * SHARD_K
+    gather_bytes = SHARD_M * (SHARD_N - (c1 - c0)) * 2          # what every rank must receive
+    return {"metric": "column_sharded_mxfp4_linear_TFLOPS", "value": flops / (res["fused_ms"] * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "ms_per_step": res["fused_ms"], **res,
+            "nccl_baseline_TFLOPS": flops / (res["nccl_ms"] * 1e-3) / 1e12,
+            "config": {"workload": f"MXFP4 linear M={SHARD_M} K={SHARD_K} N={SHARD_N}, weight rows sharded over {world} "
+                                   f"GPUs, activations replicated, complete bf16 output on every rank"},
+            "gather_bytes_per_rank": gather_bytes,
+            "nvlink_floor_ms": gather_bytes / 770e9 * 1e3, "gpu_launches": 2 * args.steps, "scaling": "strong"}
+
+
 SWEEP_ROWS, SWEEP_COLS, SWEEP_CALIB = 4096, 4096, 32768
 
 
@@ -445,6 +496,8 @@ def run_ours(args) -> None:
         hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
         hess_ffn = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
         extra = {"gemm": gemm, "hessian": hess, "hessian_hidden14336": hess_ffn, "sweep": bench_sweep(args, dev, torch)}
+        if world > 1:
+            extra["gemm_column_sharded"] = bench_sharded_gemm(args, dev, torch, dist, world, barrier)
 
     if rank == 0:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9

@@ -47,6 +47,10 @@ extern "C" {
                                    reference's runtime module does between its einsum and its
                                    quantizer (src/utils/wush_utils.py:140-149) */
 
+/* quantization formats of the entry points that take a `format` argument */
+#define WUSH_FORMAT_MXFP4 0 /* groups of 32, E8M0 scales */
+#define WUSH_FORMAT_NVFP4 1 /* groups of 16, E4M3 scales, fp32 tensor scale */
+
 /* Library / build information: compute capability the kernels were compiled for (100). */
 WUSH_API int wush_b200_arch(void);
 
@@ -222,6 +226,32 @@ WUSH_API int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b, 
 WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
 /*
+ * Block-scaled FP4 GEMM with column-sharded weights: y[:, col0 : col0 + n] = alpha * A . B_shard^T, stored into the
+ * same place of EVERY GPU's output buffer, so that after all `world` GPUs have run it each holds the complete
+ * [m, ldy] output -- the GEMM and the all-gather of its columns in one kernel (the epilogue's whole-line stores
+ * go to peer-addressable memory over NVLink; no multicast, no collective call).
+ *
+ * Replaces, for weights split by output features over GPUs, the pair matmul_*_bf16_tn_op
+ * (inference_lib/src/fp_quant/module/qutlass_ops.py:149-206) + an all-gather of the output; the reference is
+ * single-GPU and has no counterpart.
+ *
+ *   format   WUSH_FORMAT_MXFP4 / WUSH_FORMAT_NVFP4
+ *   a        packed E2M1 [m, k/2] (replicated activations); sfa blocked scales, as for wush_gemm_*_bf16_tn
+ *   b, sfb   THIS GPU's shard of the weights: packed E2M1 [n, k/2] and its blocked scales
+ *   y_all    HOST array of `world` DEVICE pointers to bf16 [m, ldy] buffers, all addressable from this GPU (e.g.
+ *            torch symmetric memory); entry `rank` is this GPU's own buffer
+ *   ldy      row stride of the buffers in elements (the unsharded N); col0 first column of this shard;
+ *            ldy % 8 == col0 % 8 == n % 8 == 0, world <= 8
+ * The caller separates the launches from the readers of the buffers with cross-GPU barriers: nobody still reads
+ * the previous contents when any GPU starts, every GPU has finished before the result is read.  Always unsplit
+ * (no workspace).
+ */
+WUSH_API int wush_gemm_fp4_bf16_tn_sharded(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
+                                           const uint8_t* sfb, const float* alpha, void* const* y_all, int world,
+                                           int rank, int64_t ldy, int64_t col0, int64_t m, int64_t n, int64_t k,
+                                           int* status, void* stream);
+
+/*
  * One block of the GPTQ / Babai column sweep, all weight rows at once.
  *
  * Replaces the part of block_transform_gptq_babai_inner after its QR factorization
@@ -245,8 +275,6 @@ WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
  * Float64 arithmetic in the reference's operation order; ties round to the even code; exact zeros encode
  * as -0 like the reference's quantizer does.
  */
-#define WUSH_FORMAT_MXFP4 0
-#define WUSH_FORMAT_NVFP4 1
 #define WUSH_SWEEP_RTN_ONLY 1
 #define WUSH_SWEEP_FAKE_F32 2
 WUSH_API int wush_gptq_block_step(const double* rn, const double* ynew, const double* qt, const double* tmat,

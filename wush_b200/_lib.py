@@ -65,6 +65,7 @@ def load() -> ctypes.CDLL:
         "wush_hessian_peer_reduce": [vp, vp, i32, i32, i64, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
+        "wush_gemm_fp4_bf16_tn_sharded": [i32, vp, vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i64, i64, vp, vp],
         "wush_gptq_block_step": [vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, vp, vp, vp, vp, vp],
         "wush_gptq_block_prepare": [vp, vp, i64, i64, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp],
     }

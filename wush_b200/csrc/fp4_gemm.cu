@@ -50,11 +50,19 @@ constexpr int EPI_WARP0 = 2, SF_WARP0 = 10, SFP_WARP = 14;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
+constexpr int MAX_PEERS = 8;
+
 struct Params {
   const uint8_t* sfa;   // blocked scales of A: ceil(M/128) row blocks x sf_atoms_k atoms of 512 B
   const uint8_t* sfb;
   const float* alpha;   // device scalar
-  __nv_bfloat16* y;     // [M, N]
+  __nv_bfloat16* y;     // [M, N] (row stride ldy); with column-sharded weights: this GPU's copy of the full output
+  // Column-sharded weights: the tile is also stored into the same place of the other GPUs' output buffers
+  // (peer-addressable memory, plain stores over NVLink), which is the all-gather of the output columns.
+  __nv_bfloat16* y_peer[MAX_PEERS];
+  int n_peers;          // entries of y_peer (0: single GPU)
+  int64_t ldy;          // row stride of the output buffers in elements (N, or the unsharded N)
+  int64_t ycol0;        // first output column of this GPU's shard inside them
   float* partial;       // [splits, M, N] when splits > 1
   int m, n, k;
   int m_blocks, n_blocks, k_blocks;   // k_blocks of BK elements (the last may be half)
@@ -235,8 +243,23 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
     for (int i = 0; i < 8; ++i) {
       const int row = rbase + i, slot = 8 * h + i;
       if (row < p.m && col < p.n)
-        *reinterpret_cast<uint4*>(p.y + (int64_t)row * p.n + col) =
+        *reinterpret_cast<uint4*>(p.y + (int64_t)row * p.ldy + p.ycol0 + col) =
             make_uint4(packed[4 * slot], packed[4 * slot + 1], packed[4 * slot + 2], packed[4 * slot + 3]);
+    }
+  }
+  // the same lines to every other GPU's buffer: whole 128-byte lines, so the NVLink packets are full
+  for (int pr = 0; pr < p.n_peers; ++pr) {
+    __nv_bfloat16* yp = p.y_peer[pr];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = col0 + (8 * h + j) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = rbase + i, slot = 8 * h + i;
+        if (row < p.m && col < p.n)
+          *reinterpret_cast<uint4*>(yp + (int64_t)row * p.ldy + p.ycol0 + col) =
+              make_uint4(packed[4 * slot], packed[4 * slot + 1], packed[4 * slot + 2], packed[4 * slot + 3]);
+      }
     }
   }
 }
@@ -745,9 +768,16 @@ static int choose_splits(int64_t tiles, int k_blocks, int sms) {
   return s < 1 ? 1 : (int)s;
 }
 
+struct Shard {               // column-sharded output: where this GPU's columns go, here and on the other GPUs
+  void* const* y_all = nullptr;   // HOST array of `world` device pointers, entry `rank` being this GPU's buffer
+  int world = 1, rank = 0;
+  int64_t ldy = 0, col0 = 0;
+};
+
 static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                        const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
-                       size_t workspace_bytes, int force_splits, int* status, cudaStream_t stream) {
+                       size_t workspace_bytes, int force_splits, int* status, cudaStream_t stream,
+                       const Shard* shard = nullptr) {
   if (!a || !b || !sfa || !sfb || !alpha || !y) return WUSH_ERR_NULL_POINTER;
   if (m < 0 || n <= 0 || k <= 0 || k % 128 != 0 || n % 8 != 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
     return WUSH_ERR_BAD_SHAPE;
@@ -758,6 +788,14 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   Params p{};
   p.sfa = sfa; p.sfb = sfb; p.alpha = alpha; p.y = (__nv_bfloat16*)y;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.ldy = n;
+  if (shard) {
+    p.ldy = shard->ldy;
+    p.ycol0 = shard->col0;
+    for (int r = 0; r < shard->world; ++r)
+      if (r != shard->rank) p.y_peer[p.n_peers++] = (__nv_bfloat16*)shard->y_all[r];
+    force_splits = 1;      // partial tiles have no peer path: the sharded GEMM always runs unsplit
+  }
   p.m_blocks = (int)((m + BM - 1) / BM);
   p.n_blocks = (int)((n + BN - 1) / BN);
   p.k_blocks = (int)((k + BK - 1) / BK);
@@ -838,7 +876,7 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
     const int64_t mn = m * n;   // n % 8 == 0, so rows stay 16-byte aligned and mn % 4 == 0
     int64_t blocks = (mn / 4 + 255) / 256;
     if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partial, alpha, p.y, mn, splits);
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partial, alpha, p.y, mn, splits);   // ldy == n here
     e = cudaGetLastError();
   }
   return (int)e;
@@ -859,6 +897,25 @@ extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const 
                                       size_t workspace_bytes, int splits, int* status, void* stream) {
   return wush::gemm::gemm_launch(true, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
                                  (cudaStream_t)stream);
+}
+
+extern "C" int wush_gemm_fp4_bf16_tn_sharded(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
+                                             const uint8_t* sfb, const float* alpha, void* const* y_all, int world,
+                                             int rank, int64_t ldy, int64_t col0, int64_t m, int64_t n, int64_t k,
+                                             int* status, void* stream) {
+  using namespace wush::gemm;
+  if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
+  if (!y_all) return WUSH_ERR_NULL_POINTER;
+  if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) return WUSH_ERR_BAD_SHAPE;
+  if (ldy < col0 + n || col0 < 0 || col0 % 8 || ldy % 8) return WUSH_ERR_BAD_SHAPE;
+  for (int r = 0; r < world; ++r) {
+    if (!y_all[r]) return WUSH_ERR_NULL_POINTER;
+    if ((uintptr_t)y_all[r] & 15) return WUSH_ERR_BAD_ALIGNMENT;
+  }
+  Shard sh;
+  sh.y_all = y_all; sh.world = world; sh.rank = rank; sh.ldy = ldy; sh.col0 = col0;
+  return gemm_launch(format == WUSH_FORMAT_NVFP4, a, b, sfa, sfb, alpha, y_all[rank], m, n, k, nullptr, 0, 1, status,
+                     (cudaStream_t)stream, &sh);
 }
 
 // ---------------------------------------------------------------------------------------------
