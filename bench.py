@@ -162,6 +162,7 @@ def workload_config(n_gpus: int) -> dict:
             "l2_policy": f"inputs ({TOKENS * HIDDEN * 2 / 1e6:.0f} MB) and outputs ({TOKENS * HIDDEN * 0.53125 / 1e6:.0f} MB) "
                          "against a 126 MB L2: larger than L2 at the default size, so no flush between iterations",
             "parallelism": f"rows sharded over {n_gpus} GPU(s), no collective",
+            "launch": "the K timed steps (K calls of the public op) are captured into one CUDA graph and replayed",
             "baseline_metric": "MXFP4 W4A4 GEMM TFLOPS + fused transform-quant GB/s; Hessian tok/s @1/2/4/8"}
 
 
@@ -174,13 +175,39 @@ HESS_TOKENS, HESS_HIDDEN = 128 * 2048, 4096
 FP4_NOMINAL_TFLOPS = 9000.0      # NVIDIA's dense FP4 figure for B200 (the 2:4-sparse figure is twice that)
 
 
-def _time_steps(fn, steps: int, torch) -> float:
+def _capture_steps(fn, steps: int, torch):
+    """`steps` calls of fn captured into one CUDA graph (the Python and dispatcher time of a call is of the
+    order of the kernels timed here, so an eager loop leaves the GPU waiting for the host).  Returns a callable
+    that replays the graph, or None when capture is not possible."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()                                   # allocator and lazy initialisation outside the capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(steps):
+                fn()
+        return graph.replay
+    except Exception as exc:                       # noqa: BLE001 - fall back to the eager loop
+        sys.stderr.write(f"bench: CUDA graph capture failed ({exc}); timing an eager loop\n")
+        torch.cuda.synchronize()
+        return None
+
+
+def _time_steps(fn, steps: int, torch, graph: bool = False) -> float:
     """Average milliseconds per call, CUDA events on the launching stream."""
+    replay = _capture_steps(fn, steps, torch) if graph else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
-    for _ in range(steps):
-        fn()
+    if replay is not None:
+        replay()
+    else:
+        for _ in range(steps):
+            fn()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
@@ -203,7 +230,7 @@ def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
     fn = lambda: ops.matmul_fp4_blocked(xq, wq, xs.view(-1), wsf.view(-1), alpha, "mx")
     for _ in range(3):
         fn()
-    ms = _time_steps(fn, args.steps, torch)
+    ms = _time_steps(fn, args.steps, torch, graph=True)
     flops = 2.0 * GEMM_M * GEMM_N * GEMM_K
     tflops = flops / (ms * 1e-3) / 1e12
     peak4 = 4.0 * peaks["bf16_tflops"]
@@ -436,13 +463,18 @@ def run_ours(args) -> None:
 
     for _ in range(warmup):
         step()
+    # the K timed steps are one CUDA graph: K calls of the public op, replayed with one launch
+    replay = _capture_steps(step, args.steps, torch)
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         barrier()
         ev0.record()
-        for _ in range(args.steps):
-            step()
+        if replay is not None:
+            replay()
+        else:
+            for _ in range(args.steps):
+                step()
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
