@@ -440,9 +440,11 @@ def run_ours(args) -> None:
     peaks, peak_kind = measured_peaks()
     warmup = max(args.warmup, 3)
 
-    if args.only in ("gemm", "hessian"):
+    if args.only in ("gemm", "hessian", "sweep"):
         if args.only == "gemm":
             res = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
+        elif args.only == "sweep":
+            res = bench_sweep(args, dev, torch)
         else:
             res = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=args.hess_hidden)
         if rank == 0:
@@ -623,7 +625,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
-    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian"],
+    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian", "sweep"],
                     help="run one section only (profiler captures of a single kernel on a small case)")
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)
