@@ -127,35 +127,39 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
   }
 }
 
-// The four MMAs of a full k-block in one instruction sequence, preceded by a non-blocking test of the
-// barrier the NEXT k-block will wait on.  A barrier test costs the issuing thread ~200 cycles even when the
-// phase is complete, and the MMA queue is shallow: with the test between two k-blocks the tensor pipe ran
-// dry for that long in every k-block.  Placed here its latency overlaps the issue of the MMAs; only the
-// result is consumed afterwards.  Returns whether the probed phase is complete.
+// The four MMAs of a full k-block in one instruction sequence, preceded by non-blocking tests of the two
+// barriers the NEXT k-block depends on (operands landed, scales in tensor memory).  A barrier test costs the
+// issuing thread ~200 cycles even when the phase is complete, and the MMA queue is shallow: with the tests
+// between two k-blocks the tensor pipe ran dry for that long in every k-block.  Placed here their latency
+// overlaps the issue of the MMAs; only the results are consumed afterwards.  Returns whether both probed
+// phases are complete.
 template <bool NV, bool PAIR>
 __device__ __forceinline__ bool umma_fp4_x4_probe(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t idesc_even,
                                                   uint32_t idesc_odd, uint32_t sfa_col, uint32_t sfb_col,
-                                                  uint32_t accumulate, uint32_t probe_bar, uint32_t probe_parity) {
+                                                  uint32_t accumulate, uint32_t probe_bar, uint32_t probe_bar2,
+                                                  uint32_t probe_parity) {
   // k-step ks: operands advance 32 bytes (2 descriptor units); MXFP4 uses scale bytes (ks & 1) * 2 of atom
   // ks >> 1, NVFP4 all four bytes of atom ks
   const uint32_t a1 = NV ? 1 : 0, a2 = NV ? 2 : 1, a3 = NV ? 3 : 1;
   uint32_t ready;
 #define WUSH_MMA4(GROUP, KIND)                                                                                     \
   asm volatile(                                                                                                    \
-      "{\n.reg .pred p, q, t;\n"                                                                                   \
+      "{\n.reg .pred p, q, q2, t;\n"                                                                               \
       "mbarrier.test_wait.parity.shared::cta.b64 q, [%21], %22;\n"                                                 \
+      "mbarrier.test_wait.parity.shared::cta.b64 q2, [%23], %22;\n"                                                \
       "setp.ne.b32 p, %20, 0;\n"                                                                                   \
       "setp.eq.b32 t, 0, 0;\n"                                                                                     \
       "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %2, %6, %10, [%12], [%16], p;\n"                      \
       "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %3, %7, %11, [%13], [%17], t;\n"                      \
       "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %4, %8, %10, [%14], [%18], t;\n"                      \
       "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %5, %9, %11, [%15], [%19], t;\n"                      \
+      "and.pred q, q, q2;\n"                                                                                       \
       "selp.u32 %0, 1, 0, q;\n}\n"                                                                                 \
       : "=r"(ready)                                                                                                \
       : "r"(d_tmem), "l"(ad), "l"(ad + 2), "l"(ad + 4), "l"(ad + 6), "l"(bd), "l"(bd + 2), "l"(bd + 4),            \
         "l"(bd + 6), "r"(idesc_even), "r"(idesc_odd), "r"(sfa_col), "r"(sfa_col + 4 * a1), "r"(sfa_col + 4 * a2),  \
         "r"(sfa_col + 4 * a3), "r"(sfb_col), "r"(sfb_col + 8 * a1), "r"(sfb_col + 8 * a2), "r"(sfb_col + 8 * a3),  \
-        "r"(accumulate), "r"(probe_bar), "r"(probe_parity)                                                         \
+        "r"(accumulate), "r"(probe_bar), "r"(probe_parity), "r"(probe_bar2)                                        \
       : "memory")
   if (NV) {
     if (PAIR) WUSH_MMA4("2", "mxf4nvf4.block_scale.block16");
@@ -372,8 +376,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
         tc_fence_after();
         for (int kb = kb0; kb < kb1; ++kb) {
-          // one wait per k-block: the feeders arrive on sf_bar only after the operands have landed too
-          if (!ready && !(ok = mbar_wait(sf_bar(s), round & 1, abort_flag))) break;
+          // fast path: the probe issued with the previous k-block saw both barriers of this one complete
+          if (!ready) {
+            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;     // operands landed
+            if (!(ok = mbar_wait(sf_bar(s), round & 1, abort_flag))) break;       // scales are in TMEM
+          }
           tc_fence_after();
           const uint32_t a0 = smem_base + s * STAGE_BYTES, b0 = a0 + A_BYTES;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
@@ -386,7 +393,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const uint32_t parity_n = (sn == 0 ? round + 1 : round) & 1;
           if (atoms == ATOMS) {
             ready = umma_fp4_x4_probe<NV, false>(tmem_base, ad, bd, make_idesc_fp4(NV, 0), make_idesc_fp4(NV, NV ? 0 : 2),
-                                                 sfa_col, sfb_col, kb > kb0, sf_bar(sn), parity_n);
+                                                 sfa_col, sfb_col, kb > kb0, full_bar(sn), sf_bar(sn), parity_n);
           } else {
             const int ksteps = atoms * (NV ? 1 : 2);   // MMAs of K = 64 in a short last k-block
             for (int ks = 0; ks < ksteps; ++ks) {
@@ -435,8 +442,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + SFB_OFF + 8 * a, vb[a][0], vb[a][1]);
         tmem_st_wait();
         tc_fence_before();
-        // the MMA issuer waits on sf_bar alone, so it must also imply "operands landed"
-        if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(sf_bar(s));
         if (++s == STAGES) { s = 0; ++round; }
@@ -631,9 +636,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         if (!(ok = mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag))) break;
         tc_fence_after();
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          // one wait per k-block: the leader's feeders arrive on sfready only after the operands of both CTAs
-          // have landed (they wait on `full` first)
-          if (!ready && !(ok = mbar_wait(sfready_bar(s), round & 1, abort_flag))) break;
+          if (!ready) {
+            if (!(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;      // operands of both CTAs landed
+            if (!(ok = mbar_wait(sfready_bar(s), round & 1, abort_flag))) break;   // scales of both CTAs in TMEM
+          }
           tc_fence_after();
           const uint32_t a0 = smem_base + s * P_STAGE_BYTES, b0 = a0 + A_BYTES;
           const int atoms = min(ATOMS, p.sf_atoms_k - kb * ATOMS);
@@ -645,7 +651,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
           if (atoms == ATOMS) {
             ready = umma_fp4_x4_probe<NV, true>(tmem_base, ad, bd, make_idesc_fp4(NV, 0, 256),
                                                 make_idesc_fp4(NV, NV ? 0 : 2, 256), sfa_col, sfb_col, kb > 0,
-                                                sfready_bar(sn), parity_n);
+                                                full_bar(sn), sfready_bar(sn), parity_n);
           } else {
             const int ksteps = atoms * (NV ? 1 : 2);
             for (int ks = 0; ks < ksteps; ++ks) {
@@ -700,7 +706,6 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
         for (int a = 0; a < ATOMS; ++a) tmem_st_x8(sfa_col + G::SFB_COL + 8 * a, vb[a][0], vb[a][1]);
         tmem_st_wait();
         tc_fence_before();
-        if (leader && !(ok = mbar_wait(full_bar(s), round & 1, abort_flag))) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(leader ? sfready_bar(s) : sflocal_bar(s));
         if (++s == P_STAGES) { s = 0; ++round; }
