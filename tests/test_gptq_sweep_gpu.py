@@ -105,3 +105,36 @@ def test_quantize_layers_splits_and_layers_run():
         y, want = layer(xt).float(), xt.float() @ w.float().T
         rel = (y - want).norm() / want.norm()
         assert rel < 0.2, rel
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_prepare_kernel_matches_torch_linear_algebra(fmt):
+    """wush_gptq_block_prepare against the same algebra done with torch.linalg in float64 (gptq.get_transform,
+    torch.linalg.qr): transforms equal up to the bf16 rounding of a few entries, R^T R = M^T M, Q^T orthogonal
+    and Q^T M = R."""
+    from wush_b200 import _lib, gptq
+    dev = torch.device("cuda:0")
+    g = wo.FORMATS[fmt]["group"]
+    nb, rows = 6, 320
+    gen = torch.Generator(device=dev).manual_seed(5)
+    m = torch.randn(nb, g, g, generator=gen, device=dev, dtype=torch.float64)
+    basis = torch.linalg.cholesky(m @ m.transpose(-2, -1) + 0.5 * torch.eye(g, device=dev, dtype=torch.float64), upper=True).contiguous()
+    y = torch.randn(nb, g, rows, generator=gen, device=dev, dtype=torch.float64) * torch.logspace(0, -2, g, device=dev, dtype=torch.float64)[None, :, None]
+    y = (torch.linalg.qr(torch.randn(nb, g, g, generator=gen, device=dev, dtype=torch.float64)).Q @ y).contiguous()
+    gram = (y @ y.transpose(-2, -1)).contiguous()
+    tm, rn, qt = (torch.empty(nb, g, g, dtype=torch.float64, device=dev) for _ in range(3))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    gptq._prepare(gram, basis, g, g * g, nb, wo.FORMATS[fmt]["group"] == 16 and _lib.FORMAT_NVFP4 or _lib.FORMAT_MXFP4,
+                  "wush", False, rows, tm, rn, qt, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want_t = gptq.get_transform(basis, y, "wush", torch.bfloat16)
+    # same sign convention on both sides; entries may differ by one bf16 step where the float64 values straddle a tie
+    rel = (tm - want_t).abs() / want_t.abs().clamp_min(1e-3)
+    assert float((rel > 2.0 ** -7).double().mean()) == 0.0
+    assert float((tm != want_t).double().mean()) < 0.02
+    mm = basis @ tm.transpose(-2, -1)
+    eye = torch.eye(g, device=dev, dtype=torch.float64)
+    assert float((qt @ qt.transpose(-2, -1) - eye).abs().max()) < 1e-12
+    assert float((qt @ mm - rn).abs().max()) < 1e-11 * float(mm.abs().max())
+    assert float(rn.tril(-1).abs().max()) == 0.0
