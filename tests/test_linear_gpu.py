@@ -72,3 +72,36 @@ def test_hadamard_linear_quantizes_its_own_weight():
     assert np.linalg.norm(y - exact) / np.linalg.norm(exact) < 0.25
     with pytest.raises(NotImplementedError):
         FPQuantConfig(forward_method="quest") and FPQuantLinear(512, 256, FPQuantConfig(forward_method="quest"), device=dev)
+
+
+@pytest.mark.parametrize("fmt,rtn", [("mxfp4", False), ("nvfp4", True)])
+def test_calibrate_sweep_export_load_forward(fmt, rtn):
+    """The whole pipeline on the GPU: Hessian from calibration activations -> column sweep (quantize_layers, two
+    layers sharing the input) -> realquant checkpoint entries -> FPQuantLinear.  The real-quant layer (fused
+    quantize + FP4 GEMM) must agree with the pseudo-quantized layer the sweep returned (same codes, same
+    transforms; the two differ only in where values are rounded to bf16)."""
+    from wush_b200 import gptq
+    from wush_b200.hessian import DistributedHessian
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    hidden, tokens = 512, 256
+    g = wo.FORMATS[fmt]["group"]
+    dh = DistributedHessian(hidden, dev)
+    for i in range(3):
+        dh.update(synth.activations(700, hidden, seed=40 + i).to(dev))
+    h = dh.finalize()
+    w1, w2 = synth.weights(256, hidden, seed=6).to(dev), synth.weights(128, hidden, seed=7).to(dev)
+    pseudo, results = gptq.quantize_layers(w1, w2, hessian=h, quant_type=fmt, transform_class="wush", force_rtn=rtn)
+    x = synth.activations(tokens, hidden, seed=50).to(dev)
+    for layer_p, res, w in zip(pseudo, results, (w1, w2)):
+        entry = gptq.export_realquant(res, fmt)
+        assert entry["qweight"].dtype == torch.uint8 and entry["forward_hadamard_matrix"].shape == (g, hidden)
+        cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=g, transform_init="wush")
+        real = FPQuantLinear(hidden, w.shape[0], cfg, bias=False, device=dev)
+        real.load_quantized(entry["qweight"], entry["scales"], entry["forward_hadamard_matrix"],
+                            entry["weight_global_scale"], entry["act_global_scale"])
+        y_real, y_pseudo = real(x).float(), layer_p(x).float()
+        rel = float((y_real - y_pseudo).norm() / y_pseudo.norm())
+        assert rel < 2e-2, rel
+        exact = x.float() @ w.float().T
+        assert float((y_real - exact).norm() / exact.norm()) < 0.25

@@ -261,3 +261,21 @@ def quantize_layers(*weights: torch.Tensor, hessian: torch.Tensor, quant_type: s
     results = [{"transform_basis": tb, "qweight": qs[i], "scale_quant": ss[i], "global_scale": res["global_scale"]}
                for i in range(len(weights))]
     return layers, results
+
+
+def export_realquant(result: dict, quant_type: str, dtype: torch.dtype = torch.bfloat16) -> dict:
+    """One layer's entry of the reference's 'realquant' checkpoint (wush_gptq.py:586-599) from a per-layer dict
+    of quantize_layers(): the names and layouts FPQuantLinear loads (`load_quantized`).  The per-group transforms
+    (C/G, G, G) become the (G, C) matrix whose column block n is T_n^T."""
+    gs = _FORMATS[quant_type]["global_scale"]
+    tb = result["transform_basis"].to(dtype)
+    matrix = tb.reshape(-1, tb.shape[-1]).t().contiguous()
+    scale = torch.tensor([gs], dtype=torch.float32)
+    return {
+        "qweight": result["qweight"].view(torch.uint8).cpu(),
+        "scales": result["scale_quant"].view(torch.uint8).cpu(),
+        "forward_hadamard_matrix": matrix.cpu(),
+        "backward_hadamard_matrix": matrix.cpu().clone(),
+        "weight_global_scale": scale.clone(),
+        "act_global_scale": scale.clone(),
+    }
