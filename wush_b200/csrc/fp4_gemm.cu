@@ -33,11 +33,6 @@
 #include "sm100.cuh"
 
 namespace wush {
-namespace gemv {   // fp4_gemv.cu: weight-streaming kernel for M <= 16
-constexpr int kNotApplicable = -1000;
-int launch_mx(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha, void* y,
-              int64_t m, int64_t n, int64_t k, cudaStream_t stream);
-}  // namespace gemv
 namespace gemm {
 
 using namespace sm100;
@@ -794,11 +789,6 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)sfa & 15) || ((uintptr_t)sfb & 15) || ((uintptr_t)y & 15))
     return WUSH_ERR_BAD_ALIGNMENT;
   if (m == 0) return WUSH_OK;
-  if (!nv && !shard && force_splits == 0 && m <= 16) {
-    // decode-sized MXFP4 problems stream the weights once through the warp-MMA kernel
-    const int rc = gemv::launch_mx(a, b, sfa, sfb, alpha, y, m, n, k, stream);
-    if (rc != gemv::kNotApplicable) return rc;
-  }
   const int group = nv ? 16 : 32;
   Params p{};
   p.sfa = sfa; p.sfb = sfb; p.alpha = alpha; p.y = (__nv_bfloat16*)y;
