@@ -440,9 +440,11 @@ def run_ours(args) -> None:
     peaks, peak_kind = measured_peaks()
     warmup = max(args.warmup, 3)
 
-    if args.only in ("gemm", "hessian", "sweep"):
+    if args.only in ("gemm", "hessian", "sweep", "sharded"):
         if args.only == "gemm":
             res = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
+        elif args.only == "sharded":
+            res = bench_sharded_gemm(args, dev, torch, dist, world, barrier)
         elif args.only == "sweep":
             res = bench_sweep(args, dev, torch)
         else:
@@ -625,7 +627,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
-    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian", "sweep"],
+    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian", "sweep", "sharded"],
                     help="run one section only (profiler captures of a single kernel on a small case)")
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)

@@ -252,8 +252,9 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
     }
   }
   // the same lines to every other GPU's buffer: whole 128-byte lines, so the NVLink packets are full
-  for (int pr = 0; pr < p.n_peers; ++pr) {
-    __nv_bfloat16* yp = p.y_peer[pr];
+  const int first = p.n_peers > 0 ? (int)((blockIdx.x + (threadIdx.x >> 5)) % p.n_peers) : 0;   // spread the warps over the peers
+  for (int i = 0; i < p.n_peers; ++i) {
+    __nv_bfloat16* yp = p.y_peer[(first + i) % p.n_peers];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int col = col0 + (8 * h + j) * 8;
@@ -797,8 +798,9 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   if (shard) {
     p.ldy = shard->ldy;
     p.ycol0 = shard->col0;
-    for (int r = 0; r < shard->world; ++r)
-      if (r != shard->rank) p.y_peer[p.n_peers++] = (__nv_bfloat16*)shard->y_all[r];
+    // every rank starts with its right-hand neighbour, so that the ranks do not all write to the same GPU at once
+    for (int i = 1; i < shard->world; ++i)
+      p.y_peer[p.n_peers++] = (__nv_bfloat16*)shard->y_all[(shard->rank + i) % shard->world];
     force_splits = 1;      // partial tiles have no peer path: the sharded GEMM always runs unsplit
   }
   p.m_blocks = (int)((m + BM - 1) / BM);
