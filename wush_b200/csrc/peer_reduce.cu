@@ -3,7 +3,7 @@
 // Every rank holds its raw lower-triangle sum in a buffer that all ranks can address (symmetric
 // memory, one process per GPU).  The lower triangle is cut into 32 x 32 tiles dealt round-robin to the
 // ranks.  For each tile it owns, a rank reads the tile from every rank's buffer with plain peer loads,
-// adds them in rank order (so all ranks end up with bit-identical results), scales by 1 / total
+// adds them (a tile is summed by its owner alone, so all ranks end up with bit-identical results), scales by 1 / total
 // tokens, and stores the finished tile and its mirror image into every rank's buffer with peer stores.
 // A given tile of any buffer is only ever touched by its owner's kernel, so the exchange can run in
 // place; the caller brackets the launch with two cross-rank barriers (all partial sums complete before
@@ -60,9 +60,11 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
     const bool in = i < p.hidden && j < p.hidden;     // hidden % 4 == 0: a float4 never straddles the edge
     if (in) {
       const int64_t off = i * p.hidden + j;
-#pragma unroll 4
+      // start with the own buffer and walk the ring, so that the ranks do not all read from the same GPU at
+      // once; a tile is summed by its owner alone, so the order is a fixed function of the tile
+#pragma unroll 8
       for (int r = 0; r < p.world; ++r) {
-        const float4 v = *reinterpret_cast<const float4*>(s_bufs[r] + off);
+        const float4 v = *reinterpret_cast<const float4*>(s_bufs[(r + p.rank) % p.world] + off);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
       acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
