@@ -9,10 +9,14 @@ algorithmic GB/s (MXFP4, per-group WUSH matrices, 16384 tokens x 14336 channels 
 resident in HBM); `e2e` is the same pass through the public host-buffer entry point (pinned H2D of
 the activations and D2H of codes+scales inside the timed region, chunked and overlapped).  `roofline` covers the quantize
 kernel, `cpu_baseline` times the CPU restatement of the reference's torch quantizer on a bounded
-sample.  `extra.gemm` (MXFP4 GEMM at 8192^3, TFLOP/s) and `extra.hessian` (262144 calibration tokens
-at hidden 4096, sharded over the GPUs with an NCCL all-reduce, tok/s) carry the other two kernels of
-the path with their own roofline and CPU-baseline objects; `extra.sweep` times the GPTQ column sweep of one
-4096 x 4096 layer.
+sample.  The other parts of the metric are top-level objects of the same line, each with its own value,
+roofline fraction, clock summary and a `parity` object (sampled outputs of the timed configuration checked
+against the float64 oracle inside the run): `quant_nvfp4`, `gemm` (MXFP4 GEMM at 8192^3), `gemm_nvfp4`,
+`decode` (the decoder-layer shape grid with M from 1 to 8192), `hessian` / `hessian_14336` (262144 calibration
+tokens sharded over the GPUs and combined over NVLink), `sweep` (GPTQ column sweep of one 4096 x 4096 layer),
+`layer_4096` (one whole layer: calibration, sweep, real-quant forward, next to the CPU pseudo-quantizer) and, on
+several GPUs, `block_70b` (the seven linears of a hidden-8192 decoder block with column-sharded weights).  A parity
+failure makes the run exit non-zero.  `extra` repeats the same objects with their long-form fields.
 
 With --impl reference the reference's CPU path (the oracle port; the reference is pure Python
 and needs its own checkout to import) is timed on the host cores for the same workload.
@@ -144,13 +148,15 @@ def run_reference(args) -> None:
     res["value"] = gbs
     line = {
         "impl": "reference", "metric": "fused_transform_quant_GBps", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * TOKENS / rows,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": workload_config(args.gpus), "cpu_baseline": res,
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "sample_rows_per_step": rows,
+        "ms_per_full_workload_extrapolated": sec * 1e3 * TOKENS / rows,
         "note": "CPU torch path of the reference restated in oracle/torch_port.py; each step is a "
-                f"{rows}-row sample of the workload, ms_per_step is scaled to the full {TOKENS} rows",
+                f"{rows}-row sample of the {TOKENS}-row workload and ms_per_step is the time of that sample "
+                "(throughput in GB/s does not depend on the sample size: rows are independent)",
     }
     print(json.dumps(line), flush=True)
 
@@ -173,6 +179,7 @@ def workload_config(n_gpus: int) -> dict:
 GEMM_M = GEMM_N = GEMM_K = 8192
 HESS_TOKENS, HESS_HIDDEN = 128 * 2048, 4096
 FP4_NOMINAL_TFLOPS = 9000.0      # NVIDIA's dense FP4 figure for B200 (the 2:4-sparse figure is twice that)
+PARITY_FAILURES: list = []       # sections whose in-run parity check failed: the run exits non-zero
 
 
 def _capture_steps(fn, steps: int, torch):
@@ -213,34 +220,195 @@ def _time_steps(fn, steps: int, torch, graph: bool = False) -> float:
     return e0.elapsed_time(e1) / steps
 
 
-def bench_gemm(args, dev, torch, ops, peaks, peak_kind) -> dict:
-    """MXFP4 W4A4 GEMM at 8192^3: operands produced by the fused quantize kernel from Gaussian
-    activations / N(0, 0.02^2) weights with a shared Hadamard transform, scales written directly in the
-    blocked layout."""
+def _parity(name: str, err: float, tol: float, what: str) -> dict:
+    ok = bool(err <= tol)
+    if not ok:
+        PARITY_FAILURES.append(name)
+    return {"max_rel": float(err), "tol": tol, "ok": ok, "what": what}
+
+
+def _sample_rows(rows: int, n: int):
+    import numpy as np
+    fixed = [0, 1, 127, 128, rows - 129, rows - 1]
+    rng = np.random.default_rng(rows)
+    return np.unique(np.concatenate([np.array(fixed) % rows, rng.choice(rows, size=max(0, n - len(fixed)), replace=False)]))
+
+
+def quant_parity(x_host, mat_np, q, sf, fmt: str, torch) -> dict:
+    """Codes and scale bytes of sampled rows of the timed output against the oracle quantizer."""
+    import numpy as np
+    from oracle import synth
+    from oracle import wush_oracle as wo
+    g = 32 if fmt == "mxfp4" else 16
+    idx = _sample_rows(x_host.shape[0], 32)
+    ref = wo.fused_transform_quant(synth.bf16_to_f64(x_host[idx]), mat_np, fmt)
+    keep = ~np.isnan(ref["fake_quant"]).any(axis=1)
+    t = torch.from_numpy(idx).to(q.device)
+    fold = lambda p: np.where(wo.unpack_e2m1_codes(p) == 8, 0, wo.unpack_e2m1_codes(p))
+    bad_q = float(np.mean(fold(q[t].cpu().numpy()[keep]) != fold(ref["e2m1"][keep])))
+    bad_s = float(np.mean(sf.view(torch.uint8)[t].cpu().numpy()[keep][:, : x_host.shape[1] // g] != ref["scale_quant"][keep]))
+    return _parity("quant_" + fmt, max(bad_q, bad_s), 1e-4,
+                   f"fraction of differing codes / scale bytes on {int(keep.sum())} sampled rows of the timed output vs "
+                   f"the float64 oracle (budget: rounding-boundary ties)")
+
+
+def bench_quant_nv(args, dev, torch, ops, peaks, peak_kind) -> dict:
+    """The quantize kernel in its NVFP4 form (groups of 16, E4M3 scales, tensor scale 10) on the benchmark shape."""
     from oracle import synth
     from wush_b200 import _lib
-    g = torch.Generator(device=dev).manual_seed(7)
-    x = torch.randn(GEMM_M, GEMM_K, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    w = (torch.randn(GEMM_N, GEMM_K, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-    had = synth.to_bf16_tensor(synth.hadamard_matrix(32)).to(dev)
-    xq, xs = ops._quantize(x, had, "mx", None, sf_layout=_lib.SF_BLOCKED)
-    wq, wsf = ops._quantize(w, had, "mx", None, sf_layout=_lib.SF_BLOCKED)
-    alpha = torch.tensor([1.0 / 9.0], device=dev)
-    del x, w
-    fn = lambda: ops.matmul_fp4_blocked(xq, wq, xs.view(-1), wsf.view(-1), alpha, "mx")
+    x_host = synth.activations(TOKENS, HIDDEN, seed=100)
+    mat_np = synth.wush_matrix(HIDDEN, 16)
+    x, mat = x_host.to(dev), synth.to_bf16_tensor(mat_np).to(dev)
+    gs = torch.tensor([10.0], device=dev)
+    lib = _lib.load()
+    q = torch.empty(TOKENS, HIDDEN // 2, dtype=torch.uint8, device=dev)
+    sf = torch.empty(TOKENS, HIDDEN // 16, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        rc = lib.wush_fused_quantize_nv(x.data_ptr(), mat.data_ptr(), HIDDEN, gs.data_ptr(), q.data_ptr(), sf.data_ptr(),
+                                        HIDDEN // 16, 0, TOKENS, HIDDEN, 0, stream)
+        assert rc == 0, rc
+
     for _ in range(3):
-        fn()
-    ms = _time_steps(fn, args.steps, torch, graph=True)
+        launch()
+    with ClockSampler(dev.index) as clocks:
+        ms = _time_steps(launch, args.steps, torch)
+    alg = algorithmic_bytes(TOKENS, HIDDEN, 16)
+    gbs = alg / (ms * 1e-3) / 1e9
+    return {"metric": "fused_transform_quant_nvfp4_GBps", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
+            "frac": gbs / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind} HBM copy bandwidth",
+            "algorithmic_bytes_per_launch": alg, "gpu_launches": args.steps,
+            "parity": quant_parity(x_host, mat_np, q, sf, "nvfp4", torch), "clocks": clocks.summary()}
+
+
+def bench_gemm(args, dev, torch, ops, peaks, peak_kind, fmt: str = "mx") -> dict:
+    """W4A4 GEMM at 8192^3: operands produced by the fused quantize kernel from Gaussian activations /
+    N(0, 0.02^2) weights with a shared Hadamard transform, scales written directly in the blocked layout."""
+    import numpy as np
+    from oracle import synth
+    from oracle import wush_oracle as wo
+    from wush_b200 import _lib
+    g = 32 if fmt == "mx" else 16
+    name = "mxfp4" if fmt == "mx" else "nvfp4"
+    gen = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(GEMM_M, GEMM_K, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    w = (torch.randn(GEMM_N, GEMM_K, generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    had = synth.to_bf16_tensor(synth.hadamard_matrix(g)).to(dev)
+    gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+    xq, xs = ops._quantize(x, had, fmt, gs, sf_layout=_lib.SF_BLOCKED)
+    wq, wsf = ops._quantize(w, had, fmt, gs, sf_layout=_lib.SF_BLOCKED)
+    a_val = 1.0 / 9.0 if fmt == "mx" else 1.0 / 100.0
+    alpha = torch.tensor([a_val], device=dev)
+    del x, w
+    fn = lambda: ops.matmul_fp4_blocked(xq, wq, xs.view(-1), wsf.view(-1), alpha, fmt)
+    for _ in range(3):
+        y = fn()
+    with ClockSampler(dev.index) as clocks:
+        ms = _time_steps(fn, args.steps, torch, graph=True)
     flops = 2.0 * GEMM_M * GEMM_N * GEMM_K
     tflops = flops / (ms * 1e-3) / 1e12
     peak4 = 4.0 * peaks["bf16_tflops"]
-    return {"metric": "mxfp4_w4a4_gemm_TFLOPS", "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms,
-            "config": {"workload": f"MXFP4 GEMM M=N=K={GEMM_M}, bf16 out, operands from the fused quantize kernel"},
-            "gpu_launches": args.steps,
-            "roofline": {"bound": "tensor", "kernel": "fp4_gemm_pair_kernel<MX>", "achieved": tflops, "peak": peak4,
-                         "unit": "TFLOP/s", "frac": tflops / peak4,
-                         "peak_kind": f"4 x {peak_kind} bf16 burst (no FP4 figure was measured)",
-                         "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None}}
+    # parity on sampled rows x columns of the timed output: the oracle dequantizes the same codes and scales
+    ra, rb = _sample_rows(GEMM_M, 24), _sample_rows(GEMM_N, 40)
+    ta, tb = torch.from_numpy(ra).to(dev), torch.from_numpy(rb).to(dev)
+    xs_rm = unblock_scales(xs.view(-1), GEMM_M, GEMM_K // g, torch)
+    ws_rm = unblock_scales(wsf.view(-1), GEMM_N, GEMM_K // g, torch)
+    want = wo.fp4_gemm(xq[ta].cpu().numpy(), xs_rm[ta].cpu().numpy(), wq[tb].cpu().numpy(), ws_rm[tb].cpu().numpy(), a_val, name)
+    got = y[ta][:, tb].double().cpu().numpy()
+    par = _parity("gemm_" + name, float(np.linalg.norm(got - want) / np.linalg.norm(want)), 1e-2,
+                  f"relative Frobenius error of {len(ra)} x {len(rb)} sampled outputs of the timed GEMM vs the float64 oracle")
+    res = {"metric": f"{name}_w4a4_gemm_TFLOPS", "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms,
+           "config": {"workload": f"{name.upper()} GEMM M=N=K={GEMM_M}, bf16 out, operands from the fused quantize kernel"},
+           "gpu_launches": args.steps,
+           "roofline": {"bound": "tensor", "kernel": f"fp4_gemm_pair_kernel<{fmt.upper()}>", "achieved": tflops, "peak": peak4,
+                        "unit": "TFLOP/s", "frac": tflops / peak4,
+                        "peak_kind": f"4 x {peak_kind} bf16 burst (no FP4 figure was measured)",
+                        "frac_of_nominal_dense_fp4": tflops / FP4_NOMINAL_TFLOPS, "traffic": None},
+           "parity": par, "clocks": clocks.summary()}
+    if fmt == "mx":
+        res["cublaslt"] = cublaslt_fp4(args, torch, xq, wq, xs, wsf, y, flops)
+    return res
+
+
+def unblock_scales(blocked, rows: int, groups: int, torch):
+    """Blocked (128 x 4 tiles) scale bytes -> row-major [rows, groups] (index arithmetic of the layout definition)."""
+    r = torch.arange(rows, device=blocked.device)[:, None]
+    gidx = torch.arange(groups, device=blocked.device)[None, :]
+    cols4 = (groups + 3) // 4
+    off = ((r // 128) * cols4 + gidx // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + gidx % 4
+    return blocked.view(torch.uint8)[off]
+
+
+def cublaslt_fp4(args, torch, xq, wq, xs, wsf, y_ours, flops) -> dict:
+    """Same-box comparator: cuBLASLt's block-scaled FP4 GEMM through torch on the same operands (1 GPU, local
+    memory).  Reported next to ours; a failure to run is recorded, not fatal."""
+    try:
+        import torch.nn.functional as F
+        a = xq.view(torch.float4_e2m1fn_x2)
+        b = wq.view(torch.float4_e2m1fn_x2).t()
+        sa, sb = xs.view(-1).view(torch.float8_e8m0fnu), wsf.view(-1).view(torch.float8_e8m0fnu)
+        kind, sw = F.ScalingType.BlockWise1x32, F.SwizzleType.SWIZZLE_32_4_4
+        fn = lambda: F.scaled_mm(a, b, sa, kind, sb, kind, swizzle_a=sw, swizzle_b=sw, output_dtype=torch.bfloat16)
+        for _ in range(3):
+            y = fn()
+        ms = _time_steps(fn, args.steps, torch, graph=True)
+        ref = y.float() * (1.0 / 9.0)
+        rel = float((y_ours.float() - ref).norm() / ref.norm())
+        return {"TFLOPS": flops / (ms * 1e-3) / 1e12, "ms_per_step": ms, "rel_diff_to_ours": rel,
+                "how": "torch.nn.functional.scaled_mm, BlockWise1x32 E8M0 scales, SWIZZLE_32_4_4, bf16 out"}
+    except Exception as exc:                       # noqa: BLE001
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+
+
+DECODE_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]      # (N, K) of the decoder layer
+DECODE_M = [1, 16, 128, 1024, 8192]
+
+
+def bench_decode(args, dev, torch, ops, peaks, peak_kind) -> dict:
+    """MXFP4 GEMM over the decoder-layer shapes of a hidden-4096 / FFN-14336 model for M from 1 to 8192.  Device
+    time per call with the calls replayed from a CUDA graph.  For M <= 16 the roofline is HBM (the weights are
+    streamed once), from 1024 on the tensor cores; in between neither is approached.  Parity: every (N, K) at
+    M = 1 and 16 against the float64 oracle on all outputs."""
+    import numpy as np
+    from oracle import wush_oracle as wo
+    grid, worst = {}, 0.0
+    gen = torch.Generator(device=dev).manual_seed(17)
+    peak4 = 4.0 * peaks["bf16_tflops"]
+    for (n, k) in DECODE_SHAPES:
+        wq = torch.randint(0, 256, (n, k // 2), generator=gen, device=dev, dtype=torch.uint8)
+        wsf = torch.randint(118, 126, (n, k // 32), generator=gen, device=dev, dtype=torch.uint8)
+        wsb = ops.to_blocked(wsf).view(-1)
+        alpha = torch.tensor([1.0 / 9.0], device=dev)
+        for m in DECODE_M:
+            xq = torch.randint(0, 256, (m, k // 2), generator=gen, device=dev, dtype=torch.uint8)
+            xsf = torch.randint(122, 130, (m, k // 32), generator=gen, device=dev, dtype=torch.uint8)
+            xsb = ops.to_blocked(xsf).view(-1)
+            fn = lambda: ops.matmul_fp4_blocked(xq, wq, xsb, wsb, alpha, "mx")
+            for _ in range(3):
+                y = fn()
+            steps = 20 if m <= 1024 else 10
+            us = _time_steps(fn, steps, torch, graph=True) * 1e3
+            wbytes = n * k / 2 + n * k / 32 + m * k / 2 + m * k / 32 + 2.0 * m * n
+            ent = {"us": us, "GBps": wbytes / us / 1e3, "TFLOPS": 2.0 * m * n * k / us / 1e6}
+            if m <= 16:
+                ent["frac_hbm"] = ent["GBps"] / peaks["hbm_gbs"]
+                want = wo.fp4_gemm(xq.cpu().numpy(), xsf.cpu().numpy(), wq.cpu().numpy(), wsf.cpu().numpy(), 1.0 / 9.0, "mxfp4")
+                got = y.double().cpu().numpy()
+                worst = max(worst, float(np.linalg.norm(got - want) / np.linalg.norm(want)))
+            elif m >= 1024:
+                ent["frac_tensor"] = ent["TFLOPS"] / peak4
+            grid[f"N{n}_K{k}_M{m}"] = ent
+    return {"metric": "mxfp4_decoder_shape_gemm_us", "unit": "us per call (device, graph replay)", "grid": grid,
+            "value": grid["N4096_K4096_M1"]["us"],
+            "config": {"workload": "MXFP4 GEMM, (N,K) of a hidden-4096 / FFN-14336 decoder layer x M in {1,16,128,1024,8192}, "
+                                   "random codes, E8M0 scales within 2^-9..2^2; one launch per call (split K finished by "
+                                   "the last-arriving warp)"},
+            "peak_kind": f"frac_hbm of {peak_kind} copy bandwidth (weights + activations + output once); frac_tensor of 4 x "
+                         f"{peak_kind} bf16 burst",
+            "gpu_launches": sum(3 + 2 * (20 if m <= 1024 else 10) for _ in DECODE_SHAPES for m in DECODE_M),
+            "parity": _parity("decode", worst, 1e-2, "worst relative Frobenius error over the four (N,K) at M = 1 and 16, all "
+                                                      "outputs vs the float64 oracle")}
 
 
 SHARD_M, SHARD_N, SHARD_K = 32768, 8192, 8192      # 16 x 2048 tokens through one hidden-8192 projection
@@ -249,7 +417,8 @@ SHARD_M, SHARD_N, SHARD_K = 32768, 8192, 8192      # 16 x 2048 tokens through on
 def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
     """MXFP4 linear layer with the weight rows sharded over the ranks (70B-shape projection: 32768 tokens,
     8192 -> 8192): GEMM with the peer-store epilogue (the all-gather of the output columns happens inside the
-    kernel) next to the local GEMM + NCCL all-gather baseline.  Activations are replicated."""
+    kernel) next to the local GEMM + NCCL all-gather baseline.  Activations are replicated.  Parity: the two paths
+    must give the same bits on every rank, and this rank's columns must equal the unsharded kernel's."""
     from oracle import synth
     from wush_b200 import _lib
     from wush_b200 import qutlass_ops as ops
@@ -264,7 +433,7 @@ def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
     w = (torch.randn(c1 - c0, SHARD_K, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
     wq, wsf = ops._quantize(w, had, "mx", None)
     del w
-    res = {}
+    res, outs = {}, {}
     for name, peer in (("fused", True), ("nccl", False)):
         layer = ColumnShardedFP4Linear(wq, wsf[: c1 - c0, : SHARD_K // 32], SHARD_N, "mx", 1.0 / 9.0, max_tokens=SHARD_M,
                                        peer=peer)
@@ -274,7 +443,7 @@ def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            layer.forward(xq, xs.view(-1))
+            out = layer.forward(xq, xs.view(-1))
         e1.record()
         barrier()
         t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
@@ -282,7 +451,14 @@ def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res[name + "_ms"] = float(t.item())
         res[name + "_path"] = "peer-store epilogue" if layer.fused else ("NCCL all-gather" if world > 1 else "local")
+        outs[name] = out[::257].clone()            # every 257th row: 128 rows spread over all row blocks
+        if name == "nccl":
+            local = ops.matmul_fp4_blocked(xq, wq, xs.view(-1), layer.ws, layer.alpha, "mx")[::257]
+            same_cols = bool(torch.equal(outs["fused"][:, c0:c1], local))
         del layer
+    bad = torch.tensor([0 if (torch.equal(outs["fused"], outs["nccl"]) and same_cols) else 1], device=dev)
+    if world > 1:
+        dist.all_reduce(bad)
     flops = 2.0 * SHARD_M * SHARD_N * SHARD_K
     gather_bytes = SHARD_M * (SHARD_N - (c1 - c0)) * 2          # what every rank must receive
     return {"metric": "column_sharded_mxfp4_linear_TFLOPS", "value": flops / (res["fused_ms"] * 1e-3) / 1e12,
@@ -291,7 +467,9 @@ def bench_sharded_gemm(args, dev, torch, dist, world, barrier) -> dict:
             "config": {"workload": f"MXFP4 linear M={SHARD_M} K={SHARD_K} N={SHARD_N}, weight rows sharded over {world} "
                                    f"GPUs, activations replicated, complete bf16 output on every rank"},
             "gather_bytes_per_rank": gather_bytes,
-            "nvlink_floor_ms": gather_bytes / 770e9 * 1e3, "gpu_launches": 2 * args.steps, "scaling": "strong"}
+            "nvlink_floor_ms": gather_bytes / 770e9 * 1e3, "gpu_launches": 2 * args.steps, "scaling": "strong",
+            "parity": _parity("sharded", float(bad.item()), 0.0, "ranks on which the fused output differs from the NCCL "
+                              "all-gather output or from the unsharded kernel on this rank's columns (128 sampled rows)")}
 
 
 SWEEP_ROWS, SWEEP_COLS, SWEEP_CALIB = 4096, 4096, 32768
@@ -310,20 +488,22 @@ def bench_sweep(args, dev, torch) -> dict:
     del x
     w = synth.weights(SWEEP_ROWS, SWEEP_COLS, seed=401).to(dev)
     out = {}
-    for name, rtn, reps in (("rtn", True, 3), ("gptq", False, 1)):
-        gptq.gptq_babai_sweep(w, h, "mxfp4", "wush", force_rtn=rtn)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(reps):
+    with ClockSampler(dev.index) as clocks:
+        for name, rtn, reps in (("rtn", True, 3), ("gptq", False, 1)):
             gptq.gptq_babai_sweep(w, h, "mxfp4", "wush", force_rtn=rtn)
-        torch.cuda.synchronize()
-        out[name + "_ms_per_layer"] = (time.perf_counter() - t0) * 1e3 / reps
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                gptq.gptq_babai_sweep(w, h, "mxfp4", "wush", force_rtn=rtn)
+            torch.cuda.synchronize()
+            out[name + "_ms_per_layer"] = (time.perf_counter() - t0) * 1e3 / reps
     nb = SWEEP_COLS // 32
     return {"metric": "column_sweep_weight_rows_per_s", "value": SWEEP_ROWS / (out["rtn_ms_per_layer"] * 1e-3),
             "unit": "rows/s", **out,
             "config": {"workload": f"W {SWEEP_ROWS}x{SWEEP_COLS} bf16 N(0,0.02^2), MXFP4, WUSH transforms, H from "
                                    f"{SWEEP_CALIB} synthetic tokens; host wall clock incl. Cholesky and all torch ops"},
-            "gpu_launches": 4 * (1 + nb), "note": "value is the round-to-nearest sweep; gptq_ms_per_layer is the "
+            "gpu_launches": 4 * (1 + nb), "clocks": clocks.summary(),
+            "note": "value is the round-to-nearest sweep; gptq_ms_per_layer is the "
             "sequential nearest-plane sweep (one wush_gptq_block_step launch per 32-column block)"}
 
 
@@ -347,8 +527,10 @@ def cpu_sweep_throughput() -> dict:
 
 
 def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=HESS_HIDDEN) -> dict:
-    """GPTQ Hessian over 128 x 2048 calibration tokens, tokens sharded over the ranks, row panels
-    all-reduced (NCCL) while the next panel is computed, then 1/N scaling + mirror."""
+    """GPTQ Hessian over 128 x 2048 calibration tokens, tokens sharded over the ranks; the ranks are combined over
+    NVLink (peer-memory / NVSwitch reduce kernel) panel by panel while later tiles are still being multiplied, then
+    the mirror image is rebuilt.  Parity: sampled 256 x 256 blocks of the timed result against a float64
+    accumulation of the same seeded shards (summed over the ranks), and all ranks must hold the same bits."""
     from wush_b200.hessian import DistributedHessian
     local = HESS_TOKENS // world
     g = torch.Generator(device=dev).manual_seed(200 + rank)
@@ -359,11 +541,16 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
         blk[:, outl] *= 50.0
         x[r0:r0 + blk.shape[0]] = blk.to(torch.bfloat16)
     del blk
+    events: list = []
+    info = {}
 
     def job():
         dh = DistributedHessian(HESS_HIDDEN, dev)
+        dh.profile = events
         dh.accumulate_overlapped(x)
         h = dh.finalize()
+        info["path"] = ("multimem (NVSwitch) reduce" if dh._peer is not None and dh._peer.mc_ptr else
+                        "peer-memory reduce" if dh._peer is not None else ("NCCL all-reduce" if world > 1 else "single GPU"))
         dh.release()          # peer-memory buffers go back to the pool for the next job
         return h
 
@@ -371,48 +558,96 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
     for _ in range(2):
         job()
     barrier()
+    del events[:]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        job()
-    e1.record()
-    barrier()
+    with ClockSampler(dev.index) as clocks:
+        e0.record()
+        for _ in range(steps):
+            h = job()
+        e1.record()
+        barrier()
     ms = e0.elapsed_time(e1) / steps
-    # kernel alone (this rank's tokens, all row panels in one launch)
-    from wush_b200 import _lib
-    lib = _lib.load()
-    h = torch.zeros(HESS_HIDDEN, HESS_HIDDEN, device=dev)
-    st = torch.cuda.current_stream().cuda_stream
-    kfn = lambda: lib.wush_hessian_accumulate(h.data_ptr(), x.data_ptr(), local, HESS_HIDDEN, 1, None, st)
-    kfn()
-    kms = _time_steps(kfn, steps, torch)
+    # the accumulation launches of the timed jobs themselves (events around them on the launching stream)
+    kms = sum(a.elapsed_time(b) for a, b in events) / max(1, len(events))
     t = torch.tensor([ms, kms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, kms = (float(v) for v in t.tolist())
+
+    # ---- parity of the timed result --------------------------------------------------------------------
+    nb = HESS_HIDDEN // 256
+    blocks = sorted({(0, 0), (nb - 1, 0), (nb - 1, nb - 1), (nb // 2, nb // 3), (nb // 3, nb // 3)})
+    worst = 0.0
+    for bi, bj in blocks:
+        xi = x[:, bi * 256:(bi + 1) * 256].double()
+        xj = x[:, bj * 256:(bj + 1) * 256].double()
+        want = xi.t() @ xj                       # float64 on this rank's tokens
+        if world > 1:
+            dist.all_reduce(want)
+        want /= HESS_TOKENS
+        got = h[bi * 256:(bi + 1) * 256, bj * 256:(bj + 1) * 256].double()
+        worst = max(worst, float((got - want).abs().max() / want.abs().max()))
+        if not torch.equal(h[bj * 256:(bj + 1) * 256, bi * 256:(bi + 1) * 256], h[bi * 256:(bi + 1) * 256, bj * 256:(bj + 1) * 256].t()):
+            worst = float("inf")                 # the mirror image must be exact
+    if world > 1:
+        # every rank must hold the same bits: compare a bit-level checksum of the whole matrix
+        cs = h.view(torch.int32).to(torch.int64).sum().reshape(1)
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if int(lo.item()) != int(hi.item()):
+            worst = float("inf")
+        w = torch.tensor([worst], dtype=torch.float64, device=dev)
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+        worst = float(w.item())
     tri_flops = float(local) * HESS_HIDDEN * (HESS_HIDDEN + 1)
     ach = tri_flops / (kms * 1e-3) / 1e12
     # a job of tens of milliseconds runs power-capped: compare with the sustained bf16 figure there
     long_job = ms > 20.0
     peak = peaks["bf16_tflops_sustained"] if long_job else peaks["bf16_tflops"]
-    segments, left = 0, local                     # kernel launches per pass over the local tokens
-    while left > 0:
-        take = left if left < 49152 else 32768
-        left -= take
-        segments += 1
-    launches_per_job = segments + 1                       # accumulate launches + finalize / peer-reduce kernel
+    from wush_b200.hessian import tile_panels, token_segments
+    segments = len(token_segments(local))
+    launches_per_job = segments + 1
     return {"metric": "hessian_tokens_per_s", "value": HESS_TOKENS / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
             "scaling": "strong", "steps": steps,
             "config": {"workload": f"H = X^T X / N over {HESS_TOKENS} tokens (128 x 2048), hidden {HESS_HIDDEN}, bf16 "
-                                   f"in / fp32 out, {local} tokens per GPU, ranks combined by a peer-memory (NVLink) reduce kernel fused "
-                                   f"with the 1/N scaling and the mirror"},
+                                   f"in / fp32 out, {local} tokens per GPU; ranks combined by: {info.get('path')}"},
+            "combine_path": info.get("path"),
             "gpu_launches": steps * launches_per_job,
             "roofline": {"bound": "tensor", "kernel": "hessian_pair_kernel", "achieved": ach, "peak": peak,
                          "unit": "TFLOP/s", "frac": ach / peak,
                          "peak_kind": f"of {peak_kind} (bf16 {'sustained: the job runs tens of ms' if long_job else 'burst'})",
                          "algorithmic_flops_per_launch": tri_flops, "kernel_ms": kms,
-                         "note": "flops of one triangle incl. diagonal, T*C*(C+1); the full-square equivalent is twice that",
-                         "traffic": None}}
+                         "note": "flops of one triangle incl. diagonal, T*C*(C+1); the full-square equivalent is twice that; "
+                                 "kernel_ms = CUDA events around the accumulation launches inside the timed jobs",
+                         "traffic": None},
+            "parity": _parity(f"hessian_{HESS_HIDDEN}", worst, 1e-5, f"max-abs error / max-abs value over {len(blocks)} sampled "
+                              "256 x 256 blocks of the timed result vs a float64 accumulation of the same shards; mirror "
+                              "exact; all ranks bit-identical"),
+            "clocks": clocks.summary()}
+
+
+def _compact(sec: dict) -> dict:
+    """The figures of a section a reader of the one-line record needs."""
+    out = {k: sec[k] for k in ("metric", "value", "unit", "ms_per_step", "combine_path", "fused_ms", "nccl_ms",
+                               "rtn_ms_per_layer", "gptq_ms_per_layer", "frac") if k in sec}
+    if "roofline" in sec:
+        out["frac"] = sec["roofline"]["frac"]
+        out["peak_kind"] = sec["roofline"]["peak_kind"]
+        if "frac_of_nominal_dense_fp4" in sec["roofline"]:
+            out["frac_of_nominal_dense_fp4"] = sec["roofline"]["frac_of_nominal_dense_fp4"]
+        if "kernel_ms" in sec["roofline"]:
+            out["kernel_ms"] = sec["roofline"]["kernel_ms"]
+    if "parity" in sec:
+        out["parity"] = {k: sec["parity"][k] for k in ("max_rel", "tol", "ok")}
+    if "clocks" in sec:
+        out["clocks"] = sec["clocks"]
+    if "cublaslt" in sec:
+        out["cublaslt_TFLOPS"] = sec["cublaslt"].get("TFLOPS", sec["cublaslt"].get("unavailable"))
+    if "grid" in sec:
+        out["grid_us"] = {k: round(v["us"], 2) for k, v in sec["grid"].items()}
+        out["frac_hbm"] = {k: round(v["frac_hbm"], 3) for k, v in sec["grid"].items() if "frac_hbm" in v}
+    return out
 
 
 def run_ours(args) -> None:
@@ -440,25 +675,29 @@ def run_ours(args) -> None:
     peaks, peak_kind = measured_peaks()
     warmup = max(args.warmup, 3)
 
-    if args.only in ("gemm", "hessian", "sweep", "sharded"):
-        if args.only == "gemm":
-            res = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
-        elif args.only == "sharded":
-            res = bench_sharded_gemm(args, dev, torch, dist, world, barrier)
-        elif args.only == "sweep":
-            res = bench_sweep(args, dev, torch)
-        else:
-            res = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=args.hess_hidden)
+    single = {"gemm": lambda: bench_gemm(args, dev, torch, ops, peaks, peak_kind),
+              "gemm_nv": lambda: bench_gemm(args, dev, torch, ops, peaks, peak_kind, "nv"),
+              "quant_nv": lambda: bench_quant_nv(args, dev, torch, ops, peaks, peak_kind),
+              "decode": lambda: bench_decode(args, dev, torch, ops, peaks, peak_kind),
+              "sharded": lambda: bench_sharded_gemm(args, dev, torch, dist, world, barrier),
+              "sweep": lambda: bench_sweep(args, dev, torch),
+              "hessian": lambda: bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind,
+                                               HESS_HIDDEN=args.hess_hidden)}
+    if args.only in single:
+        res = single[args.only]()
         if rank == 0:
             res.update({"n_gpus": world, "only": args.only, "data": "synthetic"})
             print(json.dumps(res), flush=True)
         if world > 1:
             dist.destroy_process_group()
+        if PARITY_FAILURES:
+            raise SystemExit(f"parity check failed: {PARITY_FAILURES}")
         return
 
     # ---- fused transform + quantize: every rank its own shard of rows, same matrices -------------
     x_host = synth.activations(TOKENS, HIDDEN, seed=100 + rank).pin_memory()
-    mat = synth.to_bf16_tensor(synth.wush_matrix(HIDDEN, GROUP)).to(dev)
+    mat_np = synth.wush_matrix(HIDDEN, GROUP)
+    mat = synth.to_bf16_tensor(mat_np).to(dev)
     x = x_host.to(dev)
     alg = algorithmic_bytes(TOKENS, HIDDEN)
 
@@ -466,7 +705,7 @@ def run_ours(args) -> None:
         return ops.fused_quantize_mx_wush_op(x, mat, "abs_max", False)
 
     for _ in range(warmup):
-        step()
+        out = step()
     # the K timed steps are one CUDA graph: K calls of the public op, replayed with one launch
     replay = _capture_steps(step, args.steps, torch)
     barrier()
@@ -496,6 +735,8 @@ def run_ours(args) -> None:
 
         kernel_ms = _time_steps(launch, args.steps, torch)
     clock_summary = clocks.summary()
+    quant_par = quant_parity(x_host, mat_np, out[0], out[1], "mxfp4", torch)
+    del out
 
     # end to end: pinned host activations in, codes + scales back to pinned host memory
     e2e_ms = float("nan")
@@ -519,6 +760,9 @@ def run_ours(args) -> None:
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1)
+        hq.synchronize()
+        if not (torch.equal(q_host, q.cpu()) and torch.equal(sf_host, sf.cpu())):
+            PARITY_FAILURES.append("e2e")       # the host-buffer pass must give the bytes of the single launch
 
     times = torch.tensor([ms, e2e_ms, kernel_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -528,12 +772,17 @@ def run_ours(args) -> None:
 
     extra = {}
     if not args.kernel_only and args.only == "all":
-        gemm = bench_gemm(args, dev, torch, ops, peaks, peak_kind)
-        hess = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
-        hess_ffn = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
-        extra = {"gemm": gemm, "hessian": hess, "hessian_hidden14336": hess_ffn, "sweep": bench_sweep(args, dev, torch)}
-        if world > 1:
-            extra["gemm_column_sharded"] = bench_sharded_gemm(args, dev, torch, dist, world, barrier)
+        extra["gemm"] = single["gemm"]()
+        extra["hessian"] = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind)
+        extra["hessian_14336"] = bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind, HESS_HIDDEN=14336)
+        if world == 1:
+            # single-GPU paths: measured once, not again at every N of a scaling run
+            extra["quant_nvfp4"] = single["quant_nv"]()
+            extra["gemm_nvfp4"] = single["gemm_nv"]()
+            extra["decode"] = single["decode"]()
+            extra["sweep"] = single["sweep"]()
+        else:
+            extra["sharded"] = single["sharded"]()
 
     if rank == 0:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9
@@ -564,11 +813,17 @@ def run_ours(args) -> None:
                          "kernel_ms": kernel_ms, "traffic": quant_traffic_bytes(TOKENS, HIDDEN)},
             "cpu_baseline": cpu,
             "clocks": clock_summary,
-            "extra": extra,
+            "parity": {k: quant_par[k] for k in ("max_rel", "tol", "ok")},
         }
+        for name, sec in extra.items():
+            line[name] = _compact(sec)
+        line["parity_failures"] = list(PARITY_FAILURES)
+        line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if PARITY_FAILURES:
+        raise SystemExit(f"parity check failed: {PARITY_FAILURES}")
 
 
 # DRAM bytes per launch of the quantize kernel: dram__bytes_read.sum + dram__bytes_write.sum of the ncu
@@ -627,7 +882,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
-    ap.add_argument("--only", default="all", choices=["all", "quant", "gemm", "hessian", "sweep", "sharded"],
+    ap.add_argument("--only", default="all", choices=["all", "quant", "quant_nv", "gemm", "gemm_nv", "decode", "hessian", "sweep", "sharded"],
                     help="run one section only (profiler captures of a single kernel on a small case)")
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)

@@ -55,6 +55,22 @@ extern "C" {
 WUSH_API int wush_b200_arch(void);
 
 /*
+ * Device-side errors.  The entry points that take a `status` argument (a DEVICE int, may be NULL) run kernels
+ * whose waits on asynchronous copies and tensor-core completions are bounded; if one runs out, the kernel
+ * unwinds, frees what it holds and sets *status = 1 (its output is then invalid).  One word may be shared by any
+ * number of calls.  wush_status_check synchronizes `stream`, reads the word and returns WUSH_ERR_DEVICE_TIMEOUT
+ * (clearing the word) if it was set, WUSH_OK otherwise.  The reference has no error codes; its host code raises
+ * Python exceptions (e.g. src/quantization/accumulate_hessian.py:126-127), which is what the Python layer does
+ * with this return value.
+ * wush_selftest_bounded_wait launches one tiny kernel that waits, with a limit of `max_polls` polls (at most
+ * 65536), on a barrier nothing arrives on, so that callers can test their handling of the status word; the
+ * kernel returns by itself within microseconds.
+ * Every launching entry point returns WUSH_ERR_NOT_SM100 when the current device is not compute capability 10.x.
+ */
+WUSH_API int wush_status_check(int* status_dev, void* stream);
+WUSH_API int wush_selftest_bounded_wait(int* status_dev, int max_polls, void* stream);
+
+/*
  * Fused per-group transform + MXFP4 quantization of activations or weights.
  *
  * Replaces qutlass.fusedQuantizeWushMx / qutlass.fusedQuantizeMx (abs_max method) as bound at
@@ -116,6 +132,9 @@ WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, i
 #define WUSH_HESSIAN_LOWER_ONLY 1 /* update the lower triangle (and diagonal) only, do not mirror */
 #define WUSH_HESSIAN_INPUT_F32 2  /* x is fp32 [tokens, hidden]; products are formed in TF32 (top 19 bits of each
                                      operand), as the reference's Triton kernel does for fp32 inputs */
+#define WUSH_HESSIAN_OVERWRITE 4  /* H = X^T X instead of H += X^T X: the previous contents of the updated entries are
+                                     not read, so the buffer needs no zeroing (what WUSH.update does on its first call,
+                                     src/quantization/wush_gptq.py:464-465, without the torch.zeros pass) */
 
 /*
  * GPTQ Hessian accumulation, in place:  H += X^T X.
@@ -126,7 +145,8 @@ WUSH_API int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows, i
  *
  *   h       fp32 [hidden, hidden] row-major, 16-byte aligned, read and written
  *   x       bf16 (or fp32 with WUSH_HESSIAN_INPUT_F32) [tokens, hidden] row-major, 16-byte aligned, hidden % 8 == 0
- *   flags   bitwise OR of WUSH_HESSIAN_LOWER_ONLY (the reference's save_lower_only=True) and WUSH_HESSIAN_INPUT_F32
+ *   flags   bitwise OR of WUSH_HESSIAN_LOWER_ONLY (the reference's save_lower_only=True), WUSH_HESSIAN_INPUT_F32 and
+           WUSH_HESSIAN_OVERWRITE
  *   status  optional device int, set to 1 if a bounded wait inside the kernel ran out (the result
  *           is then invalid); may be NULL
  * bf16 products are exact in fp32 and are summed in fp32 tensor-core accumulators over the tokens
@@ -146,9 +166,34 @@ WUSH_API int wush_hessian_accumulate_rows(float* h, const void* x, int64_t token
                                           int64_t row_end, int flags, int* status, void* stream);
 
 /*
+ * The lower triangle as a list of 256 x 256 tiles, in the order the accumulation kernel walks them (bands of 8
+ * row blocks, column block by column block inside a band).  Ranges of this list are the unit in which a
+ * multi-GPU job overlaps the combine of finished tiles with the accumulation of later ones.  No counterpart in
+ * the reference, which is single-GPU.
+ *   wush_hessian_tile_count      number of tiles: n (n + 1) / 2 with n = ceil(hidden / 256)
+ *   wush_hessian_tiles_per_wave  tiles the current device works on side by side (resident CTA pairs); a launch
+ *                                over a multiple of this many tiles has no partly filled last wave
+ *   wush_hessian_tile_coords     row / column block (units of 256) of entry `tile`
+ */
+WUSH_API int64_t wush_hessian_tile_count(int64_t hidden);
+WUSH_API int wush_hessian_tiles_per_wave(void);
+WUSH_API int wush_hessian_tile_coords(int64_t hidden, int64_t tile, int* row_block, int* col_block);
+
+/*
+ * H += X^T X restricted to entries [tile_begin, tile_end) of the tile list; always the CTA-pair kernel.
+ * Same arguments and flags as wush_hessian_accumulate.
+ */
+WUSH_API int wush_hessian_accumulate_tiles(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t tile_begin,
+                                           int64_t tile_end, int flags, int* status, void* stream);
+
+/* Writes the mirror image (upper triangle) of the tiles [tile_begin, tile_end) from their lower-triangle values. */
+WUSH_API int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream);
+
+/*
  * h[i][j] <- scale * h[i][j] for j <= i, and h[j][i] <- the same value: turns a lower-triangular raw sum
  * into the symmetric running mean that WUSH.update maintains (src/quantization/wush_gptq.py:467-468 applies
  * the 1/N factor on every call; applying it once here is algebraically the same).  hidden % 4 == 0.
+ * With scale == 1 the lower triangle is not rewritten (mirror only).
  */
 WUSH_API int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* stream);
 /* The same with scale = 1 / *count, `count` being a device int64 (e.g. the all-reduced token count): keeps a
@@ -156,21 +201,24 @@ WUSH_API int wush_hessian_finalize(float* h, int64_t hidden, float scale, void* 
 WUSH_API int wush_hessian_finalize_count(float* h, int64_t hidden, const int64_t* count, void* stream);
 
 /*
- * Multi-GPU combine of the Hessian over peer memory (one process per GPU, NVLink / NVSwitch).
+ * Multi-GPU combine of the Hessian over NVLink / NVSwitch (one process per GPU), for a range of the tile list.
  * No counterpart in the reference, which is single-GPU.
  *
  *   bufs    DEVICE array of `world` pointers: every rank's fp32 [hidden, hidden] buffer holding its raw
  *           lower-triangle sum, all addressable from this GPU (e.g. torch symmetric memory)
+ *   mc_buf  multicast address of the same buffers (one address that reaches all of them through the NVSwitch),
+ *           or NULL.  Given: the sums are formed by multimem.ld_reduce inside the switch and delivered by
+ *           multimem.st; NULL: plain peer loads and stores
  *   counts  DEVICE array of `world` pointers to each rank's int64 local token count (peer-addressable)
- * On return (stream order) every rank's buffer holds, for the 32x32 tiles this rank owns (tile t belongs to
- * rank t % world), the sum over ranks divided by the total token count, lower triangle and mirror image.
- * Once EVERY rank has run it, all buffers hold the complete symmetric matrix, bit-identical on all ranks.
- * The caller must separate the launches from the producers and consumers of the buffers with cross-rank
- * barriers: all ranks' partial sums complete before any rank starts, all ranks done before the result is
- * read.  hidden % 4 == 0, world <= 16.
+ * The 32 x 32 sub-tiles of the range are dealt round-robin to the ranks.  On return (stream order) every
+ * rank's buffer holds, for the sub-tiles this rank owns, the sum over ranks divided by the total token count
+ * (lower triangle only; wush_hessian_mirror_tiles rebuilds the rest locally).  Once EVERY rank has run it, all
+ * buffers hold the same bits for the range.  The caller separates the launches from the producers and consumers
+ * of the range with cross-rank barriers: all ranks' partial sums of the range complete before any rank starts,
+ * all ranks done before the result is read.  hidden % 4 == 0, world <= 16.
  */
-WUSH_API int wush_hessian_peer_reduce(float* const* bufs, const int64_t* const* counts, int rank, int world,
-                                      int64_t hidden, void* stream);
+WUSH_API int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const int64_t* const* counts, int rank,
+                                      int world, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream);
 
 /*
  * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.
@@ -185,12 +233,16 @@ WUSH_API int wush_hessian_peer_reduce(float* const* bufs, const int64_t* const* 
  *              hold finite scale bytes (zero is fine)
  *   alpha      device pointer to one fp32 (1 / (weight_global_scale * act_global_scale) in the reference)
  *   y          bf16 [m, n] row-major, 16-byte aligned; n % 8 == 0, k % 128 == 0
- *   workspace  device scratch for split-K partial tiles (fp32 [splits, m, n]); needed only when few output
- *              tiles exist (small m).  wush_gemm_workspace_bytes() gives the size the heuristic wants; with a
- *              smaller (or NULL) workspace the GEMM runs unsplit.
+ *   workspace  device scratch for the split-K partial tiles (fp32 [splits, m, n], 16-byte aligned, contents
+ *              irrelevant); needed only when few output tiles exist (small m).  wush_gemm_workspace_bytes() gives
+ *              the size the heuristic wants; with a smaller (or NULL) workspace the GEMM runs unsplit.
  *   splits     0 = choose automatically; > 0 forces that many K splits (fails if the workspace is too small)
  *   status     optional device int set to 1 if a bounded wait inside the kernel ran out; may be NULL
- * fp32 accumulation over the whole K range; one rounding to bf16 at the end.
+ * fp32 accumulation over the whole K range; one rounding to bf16 at the end.  Split K is one launch: every CTA
+ * writes its partial block, and the one that arrives last at the block's counter adds the partials in split order
+ * (the result does not depend on which one that is) and writes the output.  The counters are the library's own
+ * (a ring in device memory, a fresh segment per launch, zero before and after it); the first split-K call on a
+ * device looks up the ring's address and should be made outside any stream capture.
  */
 WUSH_API int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                     const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
@@ -199,18 +251,37 @@ WUSH_API int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const ui
                                     const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
                                     size_t workspace_bytes, int splits, int* status, void* stream);
 /*
+ * The same GEMM with the neighbouring element-wise steps of the layer folded into its epilogue, and explicit row
+ * strides.  Replaces, in FPQuant4x16NoMasterFn.forward (inference_lib/src/fp_quant/module/linear_fns.py:514-525),
+ * the sequence forward_gemm(...) ; y += bias, and the residual addition that follows the o_proj / down_proj layers
+ * of a decoder block.  The roundings of the unfused sequence are kept, so the result is bit-identical to it:
+ *   y = bf16(alpha * acc);  if bias: y = bf16(y + bias[col]);  if residual: y = bf16(y + residual[row, col])
+ *
+ *   format     WUSH_FORMAT_MXFP4 / WUSH_FORMAT_NVFP4
+ *   bias       bf16 [n] or NULL;  residual  bf16 [m, ldr] or NULL (may be y itself: every element is read before it
+ *              is written, by the same thread);  ldr, ldy  row strides in elements (0 = n); multiples of 8
+ * Everything else as for wush_gemm_mxf4_bf16_tn.
+ */
+WUSH_API int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
+                                         const uint8_t* sfb, const float* alpha, const void* bias, const void* residual,
+                                         int64_t ldr, void* y, int64_t ldy, int64_t m, int64_t n, int64_t k,
+                                         void* workspace, size_t workspace_bytes, int splits, int* status, void* stream);
+
+/*
  * Split-K MXFP4 GEMM for callers that must not allocate device memory.  (No counterpart in the reference.)
  *
  * Some hosts of this library cannot call cudaMalloc on the path where the GEMM runs: a serving loop whose
  * memory is fully carved up at start-up, a plugin running inside another framework's stream-ordered pool, code
  * replayed from a captured graph.  For small-M (decode) shapes the GEMM wants scratch for its split-K partial
  * tiles; this entry point keeps that scratch in a fixed array inside the library (WUSH_GEMM_STATIC_SCRATCH_BYTES
- * of device memory per GPU that loads the library, held until the process exits), so the caller passes inputs
- * and the output only.  Same arithmetic and argument meaning as wush_gemm_mxf4_bf16_tn with a workspace.
+ * of device memory per GPU that loads the library, held until the process exits), so the caller passes inputs and
+ * the output only.  Same arithmetic and argument meaning as
+ * wush_gemm_mxf4_bf16_tn with a workspace.
  *
  *   splits   0 = choose (at least 2, reduced until the partial tiles fit); >= 2 forces a value
- * Returns WUSH_ERR_TOO_LARGE when splits * m * n fp32 values do not fit in the array, WUSH_ERR_BAD_FLAG when K is
- * too short to be split (fewer than 2 blocks of 256) or `splits` is out of range.
+ * Returns WUSH_ERR_TOO_LARGE when splits * m * n fp32 values do not fit in the array (or the problem has more than
+ * 256 output tiles), WUSH_ERR_BAD_FLAG when K is too short to be split (fewer than 2 blocks of 256) or `splits`
+ * is out of range.
  * Rules: (1) the first call on each device looks up the array's device address (cudaGetSymbolAddress) and caches
  * it; make that first call outside any stream capture.  (2) Every call on a device uses the same array: calls
  * that can overlap on the GPU (different streams without ordering) race and corrupt each other; serialize them.

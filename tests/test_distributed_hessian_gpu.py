@@ -64,22 +64,25 @@ def test_update_staging_matches_direct_launches():
     assert np.linalg.norm(hf - w3) <= 2e-3 * np.linalg.norm(w3)
 
 
-def _worker(rank, world, port, out, peer):
+def _worker(rank, world, port, out, peer, multimem, per_panel, tokens0):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      WUSH_B200_HESSIAN_PEER="1" if peer else "0")
+                      WUSH_B200_HESSIAN_PEER="1" if peer else "0", WUSH_B200_HESSIAN_MULTIMEM="1" if multimem else "0",
+                      WUSH_B200_HESSIAN_TILES_PER_PANEL=str(per_panel))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     from wush_b200.hessian import DistributedHessian
-    x = synth.activations(1024 + 256 * rank, 1024, seed=70 + rank).to(dev)
+    x = synth.activations(tokens0 + 256 * rank, 1024, seed=70 + rank).to(dev)
     dh = DistributedHessian(1024, dev, panels=4)
     assert (dh._peer is not None) == peer
+    if peer and rank == 0:
+        print(f"multicast address available: {bool(dh._peer.mc_ptr)} (asked for: {multimem})", flush=True)
     dh.accumulate_overlapped(x)
     h = dh.finalize()
     torch.cuda.synchronize()
-    assert dh.num_samples == sum(1024 + 256 * r for r in range(world))
+    assert dh.num_samples == sum(tokens0 + 256 * r for r in range(world))
     # every rank must hold the same bits
     mine = h.clone()
     ref = mine.clone()
@@ -88,25 +91,64 @@ def _worker(rank, world, port, out, peer):
     if rank == 0:
         np.save(out, h.cpu().numpy())
     dh.release()
-    # second job on the pooled buffer (update path)
+    # second job on the pooled buffer (update path: one combine over the whole tile list)
     dh2 = DistributedHessian(1024, dev)
     dh2.update(x[:512])
     dh2.update(x[512:])
     h2 = dh2.finalize()
     torch.cuda.synchronize()
     assert (h2 - mine).abs().max() <= 1e-5 * mine.abs().max()
+    assert torch.equal(h2, h2.t())
+    dh2.release()
+    # third job: the same tokens again must reproduce the first result bit for bit (no state left in the pool)
+    dh3 = DistributedHessian(1024, dev, panels=4)
+    dh3.accumulate_overlapped(x)
+    h3 = dh3.finalize()
+    torch.cuda.synchronize()
+    if tokens0 <= 32768:
+        assert torch.equal(h3, mine)
+    else:
+        # launches that add to an existing sum may split the tokens and combine the splits with atomic adds
+        assert (h3 - mine).abs().max() <= 1e-6 * mine.abs().max()
     dist.barrier()
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("peer", [True, False])
-def test_two_gpu_hessian(tmp_path, peer):
-    """peer=True: ranks combined by the peer-memory kernel; False: NCCL all-reduce of row panels."""
+@pytest.mark.parametrize("peer,multimem,per_panel,tokens0", [(True, True, 0, 1024), (True, False, 3, 1024), (True, True, 4, 50000),
+                                                             (False, False, 0, 1024)])
+def test_two_gpu_hessian(tmp_path, peer, multimem, per_panel, tokens0):
+    """peer=True: ranks combined by the reduce kernel over NVLink (multimem: sums formed inside the NVSwitch when
+    a multicast address is available; per_panel > 0: the tile list is combined in several overlapped panels;
+    50000 tokens: two 32768-token segments per rank); peer=False: NCCL all-reduce of row panels."""
     import torch.multiprocessing as mp
     out = str(tmp_path / "h.npy")
-    mp.spawn(_worker, args=(2, 29650 + os.getpid() % 300 + (7 if peer else 0), out, peer), nprocs=2, join=True)
+    port = 29650 + os.getpid() % 300 + 7 * per_panel + (3 if multimem else 0)
+    mp.spawn(_worker, args=(2, port, out, peer, multimem, per_panel, tokens0), nprocs=2, join=True)
     got = np.load(out).astype(np.float64)
-    want = wo.wush_update_sequence([synth.bf16_to_f64(synth.activations(1024 + 256 * r, 1024, seed=70 + r)) for r in range(2)])
+    want = wo.wush_update_sequence([synth.bf16_to_f64(synth.activations(tokens0 + 256 * r, 1024, seed=70 + r)) for r in range(2)])
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
     assert np.array_equal(got, got.T)
+
+
+def test_layers_on_the_second_gpu_of_one_process():
+    """One process driving two GPUs (layers placed on cuda:0 and cuda:1): the kernels' shared-memory opt-in and
+    cluster occupancy are per device, so the first launch on the second device must set them up again."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from wush_b200 import qutlass_ops as ops
+    from wush_b200.hessian import accumulate_hessian
+    outs = []
+    for d in (0, 1):
+        dev = torch.device("cuda", d)
+        x = synth.activations(300, 512, seed=3).to(dev)
+        had = synth.to_bf16_tensor(synth.hadamard_matrix(32)).to(dev)
+        q, sf = ops._quantize(x, had, "mx", None, sf_layout=1)
+        wq, wsf = ops._quantize(synth.weights(256, 512, seed=4).to(dev), had, "mx", None, sf_layout=1)
+        y = ops.matmul_fp4_blocked(q, wq, sf.view(-1), wsf.view(-1), torch.tensor([1 / 9.0], device=dev), "mx")
+        y16 = ops.matmul_fp4_blocked(q[:16], wq, sf.view(-1), wsf.view(-1), torch.tensor([1 / 9.0], device=dev), "mx")
+        h = accumulate_hessian(torch.zeros(512, 512, device=dev), x)
+        torch.cuda.synchronize(dev)
+        outs.append((q.cpu(), y.cpu(), y16.cpu(), h.cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

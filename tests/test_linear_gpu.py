@@ -40,7 +40,9 @@ def test_wush_linear_end_to_end(fmt):
     cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=g, transform_init="wush")
     layer = FPQuantLinear(hidden, rows_out, cfg, bias=True, device=dev)
     mat = wo.transform_to_matrix(t)
-    layer.load_quantized(torch.from_numpy(wq["e2m1"]), torch.from_numpy(wq["scale_quant"]), torch.from_numpy(mat))
+    gs = wo.FORMATS[fmt]["global_scale"]       # what exported checkpoints carry (wush_gptq.py:588)
+    layer.load_quantized(torch.from_numpy(wq["e2m1"]), torch.from_numpy(wq["scale_quant"]), torch.from_numpy(mat),
+                         torch.tensor([gs]), torch.tensor([gs]))
     bias = torch.linspace(-1, 1, rows_out, dtype=torch.bfloat16, device=dev)
     layer.bias.data.copy_(bias)
     x = synth.activations(tokens, hidden, seed=90)
@@ -49,7 +51,6 @@ def test_wush_linear_end_to_end(fmt):
     assert y.shape == (2, tokens // 2, rows_out) and y.dtype == torch.bfloat16
     got = y.double().cpu().numpy().reshape(tokens, rows_out)
     xq = wo.fused_transform_quant(synth.bf16_to_f64(x), mat, fmt)
-    gs = wo.FORMATS[fmt]["global_scale"]
     want = wo.fp4_gemm(xq["e2m1"], xq["scale_quant"], wq["e2m1"], wq["scale_quant"], 1.0 / (gs * gs), fmt)
     want = want + bias.double().cpu().numpy()[None, :]
     assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
@@ -105,3 +106,69 @@ def test_calibrate_sweep_export_load_forward(fmt, rtn):
         assert rel < 2e-2, rel
         exact = x.float() @ w.float().T
         assert float((y_real - exact).norm() / exact.norm()) < 0.25
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_state_dict_loading_matches_load_quantized(fmt):
+    """The reference's checkpoint protocol copies qweight / scales / matrices / global scales into the module's
+    buffers through load_state_dict; the layer must then behave exactly like one filled by load_quantized(),
+    also after a second, different state dict (nothing derived from the old buffers may survive) and after
+    pre_forward(), which the loader calls on every layer."""
+    from wush_b200 import gptq
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    hidden, rows_out = 512, 256
+    g = wo.FORMATS[fmt]["group"]
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=g, transform_init="wush")
+    x = synth.activations(96, hidden, seed=3).to(dev)
+    entries = []
+    for seed in (11, 12):
+        w = synth.weights(rows_out, hidden, seed=seed).to(dev)
+        _, results = gptq.quantize_layers(w, hessian=None, quant_type=fmt, transform_class="hadamard", force_rtn=True)
+        entries.append(gptq.export_realquant(results[0], fmt))
+    ref_layers = []
+    for e in entries:
+        ref = FPQuantLinear(hidden, rows_out, cfg, bias=False, device=dev)
+        ref.load_quantized(e["qweight"], e["scales"], e["forward_hadamard_matrix"], e["weight_global_scale"],
+                           e["act_global_scale"])
+        ref_layers.append(ref)
+    layer = FPQuantLinear(hidden, rows_out, cfg, bias=False, device=dev)
+    for e, ref in zip(entries, ref_layers):
+        missing = layer.load_state_dict(e, strict=False)
+        assert not missing.unexpected_keys
+        layer.pre_forward()
+        assert layer.weight is None
+        assert torch.equal(layer(x), ref(x))
+    assert not torch.equal(ref_layers[0](x), ref_layers[1](x))
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("tokens", [8, 300])
+def test_bias_and_residual_in_the_gemm_epilogue_are_bit_identical_to_separate_adds(fmt, tokens):
+    """tokens = 8 runs the split-K kernel (the last-arriving warp finishes the tile), 300 the CTA-pair kernel."""
+    from wush_b200 import qutlass_ops as ops
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    hidden, rows_out = 1024, 384
+    g = wo.FORMATS[fmt]["group"]
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=g, transform_init="hadamard")
+    layer = FPQuantLinear(hidden, rows_out, cfg, bias=True, device=dev)
+    layer.weight.data.copy_(synth.weights(rows_out, hidden, seed=21).to(dev))
+    layer.bias.data.copy_(torch.randn(rows_out, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16))
+    layer.pre_forward()
+    x = synth.activations(tokens, hidden, seed=22).to(dev)
+    res = synth.activations(tokens, rows_out, seed=23).to(dev)
+    fused = layer(x, residual=res)
+    scales_blocked, alpha = layer._derived()
+    xq, xs = ops._quantize(x, layer.forward_hadamard_matrix, "mx" if fmt == "mxfp4" else "nv",
+                           layer.act_global_scale.float() if fmt == "nvfp4" else None, sf_layout=1)
+    plain = ops.matmul_fp4_blocked(xq, layer.qweight, xs.view(-1), scales_blocked.view(-1), alpha,
+                                   "mx" if fmt == "mxfp4" else "nv")
+    want = plain + layer.bias           # bf16 tensor arithmetic: one rounding per step, as in the reference
+    want = want + res
+    assert torch.equal(fused, want)
+    # in place: the residual buffer receives the result
+    buf = res.clone()
+    ops.matmul_fp4_blocked(xq, layer.qweight, xs.view(-1), scales_blocked.view(-1), alpha,
+                           "mx" if fmt == "mxfp4" else "nv", bias=layer.bias, residual=buf, out=buf)
+    assert torch.equal(buf, want)

@@ -23,6 +23,7 @@ SF_ROW_MAJOR, SF_BLOCKED = 0, 1
 QUANT_ROUND_BF16 = 1
 HESSIAN_LOWER_ONLY = 1
 HESSIAN_INPUT_F32 = 2
+HESSIAN_OVERWRITE = 4
 FORMAT_MXFP4, FORMAT_NVFP4 = 0, 1
 SWEEP_RTN_ONLY, SWEEP_FAKE_F32 = 1, 2
 TRANSFORMS = {"identity": 0, "hadamard": 1, "wush": 2, "wus": 3, "given": 4}
@@ -62,7 +63,15 @@ def load() -> ctypes.CDLL:
         "wush_hessian_accumulate_rows": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
         "wush_hessian_finalize": [vp, i64, ctypes.c_float, vp],
         "wush_hessian_finalize_count": [vp, i64, vp, vp],
-        "wush_hessian_peer_reduce": [vp, vp, i32, i32, i64, vp],
+        "wush_hessian_peer_reduce": [vp, vp, vp, i32, i32, i64, i64, i64, vp],
+        "wush_hessian_accumulate_tiles": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
+        "wush_hessian_mirror_tiles": [vp, i64, i64, i64, vp],
+        "wush_hessian_tiles_per_wave": [],
+        "wush_hessian_tile_coords": [i64, i64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+        "wush_status_check": [vp, vp],
+        "wush_selftest_bounded_wait": [vp, i32, vp],
+        "wush_gemm_fp4_bf16_tn_fused": [i32, vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, vp,
+                                        ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_fp4_bf16_tn_sharded": [i32, vp, vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i64, i64, vp, vp],
@@ -77,6 +86,8 @@ def load() -> ctypes.CDLL:
     lib.wush_gemm_mxf4_bf16_tn_noalloc.restype = ctypes.c_int
     lib.wush_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.wush_gemm_workspace_bytes.restype = ctypes.c_size_t
+    lib.wush_hessian_tile_count.argtypes = [i64]
+    lib.wush_hessian_tile_count.restype = ctypes.c_int64
     _lib = lib
     return lib
 
@@ -84,6 +95,57 @@ def load() -> ctypes.CDLL:
 def check(rc: int, what: str) -> None:
     if rc == 0:
         return
+    if rc in (-6, -7):
+        raise WushB200Error(f"{what}: {ERRORS[rc]}")
     if rc < 0:
         raise WushB200Error(f"{what}: rejected argument ({ERRORS.get(rc, rc)})")
     raise WushB200Error(f"{what}: CUDA error {rc}")
+
+
+# --------------------------------------------------------------------------------------------
+# per-device state shared by the ops: the status word of the bounded waits, split-K workspaces
+# --------------------------------------------------------------------------------------------
+_status_words: dict = {}
+_workspaces: dict = {}
+
+
+def status_word(device):
+    """The int32 device word every kernel launch of this process reports a run-out wait into (one per
+    device, allocated on first use and never freed)."""
+    import torch
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(key)
+    if w is None:
+        w = _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return w
+
+
+def check_status(device, what: str = "kernel") -> None:
+    """Synchronize the current stream of `device` and raise WushB200Error if any kernel launched so far reported
+    a device-side timeout (its output is invalid).  Called at the points where the host waits anyway
+    (HostQuantizer.synchronize, DistributedHessian.num_samples, the column sweep) and after every op when the
+    environment variable WUSH_B200_CHECK_STATUS=1 is set."""
+    import torch
+    w = status_word(device)
+    with torch.cuda.device(w.device):
+        rc = load().wush_status_check(w.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    check(rc, what)
+
+
+CHECK_EVERY_OP = os.environ.get("WUSH_B200_CHECK_STATUS", "0") == "1"
+
+
+def gemm_workspace(device, nbytes: int):
+    """Split-K scratch for the current stream of `device` (contents irrelevant): grown on demand and reused by
+    later calls on that stream.  While the stream is being captured into a CUDA graph the scratch comes from the
+    graph's own memory pool instead, so that it lives exactly as long as the graph."""
+    import torch
+    device = torch.device(device)
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        w = _workspaces[key] = torch.empty(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
+    return w

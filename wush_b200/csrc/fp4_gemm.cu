@@ -51,6 +51,11 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
 constexpr int MAX_PEERS = 8;
+// Split K: one arrival counter per (tile, epilogue warp).  The counters live in a ring inside the library: zero when
+// the library is loaded, returned to zero by every launch, a fresh segment per launch so that launches running side
+// by side on different streams do not share any (at most kCounterRing / 8 tiles can be in flight at once).
+constexpr int kMaxCounters = 2048;            // per launch: 256 tiles
+constexpr int kCounterRing = 1 << 16;
 
 struct Params {
   const uint8_t* sfa;   // blocked scales of A: ceil(M/128) row blocks x sf_atoms_k atoms of 512 B
@@ -64,6 +69,12 @@ struct Params {
   int64_t ldy;          // row stride of the output buffers in elements (N, or the unsharded N)
   int64_t ycol0;        // first output column of this GPU's shard inside them
   float* partial;       // [splits, M, N] when splits > 1
+  unsigned int* counters;  // splits > 1: this launch's segment of the arrival-counter ring, zero before and after
+  // optional epilogue terms, applied in the reference's order with its roundings (linear_fns.py:514-525):
+  // y = bf16(alpha * acc); y = bf16(y + bias[col]); y = bf16(y + residual[row, col])
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* residual;   // [M, ldr] or null (may alias y)
+  int64_t ldr;
   int m, n, k;
   int m_blocks, n_blocks, k_blocks;   // k_blocks of BK elements (the last may be half)
   int splits;           // CTAs sharing the K range of one tile
@@ -214,6 +225,22 @@ __device__ __forceinline__ void transpose_chunks_8x8(uint32_t (&v)[64], int lane
   }
 }
 
+// 8 packed bf16 values += 8 packed bf16 values, each sum rounded to bf16 (what `y += bias` does on bf16 tensors)
+__device__ __forceinline__ uint4 add_bf16x8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const uint32_t* pa = &a.x;
+  const uint32_t* pb = &b.x;
+  uint32_t* po = &o.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[i]));
+    const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pb[i]));
+    const __nv_bfloat162 r = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+    po[i] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  return o;
+}
+
 // Epilogue of one warp: every lane drains its row x 128 accumulator columns as packed bf16 (scaled by alpha)
 // and the accumulator is released through `release` (after a warp sync).  A lane-per-row store would touch 32
 // different lines per instruction (4096 L1 wavefronts per tile, which was measured to stall the scale feeders
@@ -240,6 +267,26 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
   release();
   transpose_chunks_8x8(packed, lane);
   const int j = lane & 7, rbase = row0 + (lane & ~7);
+  // bias and residual are added to the bf16 values after the transposition: their loads are then whole lines too
+  if (p.bias != nullptr || p.residual != nullptr) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = col0 + (8 * h + j) * 8;
+      if (col >= p.n) continue;
+      uint4 bv = make_uint4(0, 0, 0, 0);
+      if (p.bias != nullptr) bv = *reinterpret_cast<const uint4*>(p.bias + col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = rbase + i, slot = 8 * h + i;
+        if (row >= p.m) continue;
+        uint4 v = make_uint4(packed[4 * slot], packed[4 * slot + 1], packed[4 * slot + 2], packed[4 * slot + 3]);
+        if (p.bias != nullptr) v = add_bf16x8(v, bv);
+        if (p.residual != nullptr)
+          v = add_bf16x8(v, *reinterpret_cast<const uint4*>(p.residual + (int64_t)row * p.ldr + col));
+        packed[4 * slot] = v.x; packed[4 * slot + 1] = v.y; packed[4 * slot + 2] = v.z; packed[4 * slot + 3] = v.w;
+      }
+    }
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int col = col0 + (8 * h + j) * 8;          // n % 8 == 0: a chunk never straddles the edge
@@ -253,8 +300,8 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
   }
   // the same lines to every other GPU's buffer: whole 128-byte lines, so the NVLink packets are full
   const int first = p.n_peers > 0 ? (int)((blockIdx.x + (threadIdx.x >> 5)) % p.n_peers) : 0;   // spread the warps over the peers
-  for (int i = 0; i < p.n_peers; ++i) {
-    __nv_bfloat16* yp = p.y_peer[(first + i) % p.n_peers];
+  for (int pi = 0; pi < p.n_peers; ++pi) {
+    __nv_bfloat16* yp = p.y_peer[(first + pi) % p.n_peers];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int col = col0 + (8 * h + j) * 8;
@@ -266,6 +313,49 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
               make_uint4(packed[4 * slot], packed[4 * slot + 1], packed[4 * slot + 2], packed[4 * slot + 3]);
       }
     }
+  }
+}
+
+// Split K: the warp that arrives last at a (tile, warp) counter adds the fp32 partial blocks of all splits (in
+// split order, so the result does not depend on who is last) and writes the bf16 output rows of its 32 x 128
+// block: lane l owns columns 4l .. 4l+3 of every row, so loads are 512 and stores 256 contiguous bytes per row.
+__device__ __forceinline__ void splitk_finish(const Params& p, int row0, int col0, float alpha, int lane) {
+  const int col = col0 + 4 * lane;
+  if (col >= p.n) return;                       // n % 8 == 0: groups of 4 never straddle the edge
+  const int64_t mn = (int64_t)p.m * p.n;
+  float2 b01 = make_float2(0.f, 0.f), b23 = make_float2(0.f, 0.f);
+  if (p.bias != nullptr) {
+    const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + col);
+    b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.x));
+    b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.y));
+  }
+  const int rows = min(32, p.m - row0);
+  for (int r = 0; r < rows; ++r) {
+    const float* src = p.partial + (int64_t)(row0 + r) * p.n + col;
+    float4 acc = __ldcg(reinterpret_cast<const float4*>(src));
+    for (int s = 1; s < p.splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)s * mn));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * alpha, acc.y * alpha);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * alpha, acc.w * alpha);
+    if (p.bias != nullptr) {
+      const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+      lo = __floats2bfloat162_rn(l.x + b01.x, l.y + b01.y);
+      hi = __floats2bfloat162_rn(h.x + b23.x, h.y + b23.y);
+    }
+    if (p.residual != nullptr) {
+      const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + (int64_t)(row0 + r) * p.ldr + col);
+      const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.x));
+      const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.y));
+      const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+      lo = __floats2bfloat162_rn(l.x + r01.x, l.y + r01.y);
+      hi = __floats2bfloat162_rn(h.x + r23.x, h.y + r23.y);
+    }
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.y + (int64_t)(row0 + r) * p.ldy + p.ycol0 + col) = o;
   }
 }
 
@@ -487,6 +577,18 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar);
+        // count this warp's block as delivered; the last of the `splits` warps sums them (no second kernel)
+        __threadfence();
+        __syncwarp();
+        unsigned int prev = 0;
+        unsigned int* ctr = p.counters + ((mb * p.n_blocks + nb) * 8 + (warp - EPI_WARP0));
+        if (lane == 0) prev = atomicAdd(ctr, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == (unsigned int)p.splits - 1u) {
+          __threadfence();
+          if (row - lane < p.m) splitk_finish(p, row - lane, col0, alpha, lane);
+          if (lane == 0) *ctr = 0u;          // the counters are zero again when the launch ends
+        }
       }
     }
   }
@@ -746,32 +848,45 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
 
-// Sum the per-split fp32 partial tiles, scale, round to bf16.
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ alpha,
-                                     __nv_bfloat16* __restrict__ y, int64_t mn, int splits) {
-  const float a = *alpha;
-  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < mn; i += (int64_t)gridDim.x * blockDim.x * 4) {
-    float4 acc = *reinterpret_cast<const float4*>(partial + i);
-    for (int s = 1; s < splits; ++s) {
-      const float4 v = *reinterpret_cast<const float4*>(partial + (int64_t)s * mn + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * a, acc.y * a), hi = __floats2bfloat162_rn(acc.z * a, acc.w * a);
-    uint2 o;
-    o.x = *reinterpret_cast<const uint32_t*>(&lo);
-    o.y = *reinterpret_cast<const uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(y + i) = o;
-  }
-}
-
 // K splits for a problem: enough CTAs to occupy the machine when there are few output tiles
 // (small M: the GEMM streams the weights once and is HBM-bound), at least 2 k-blocks per split.
 static int choose_splits(int64_t tiles, int k_blocks, int sms) {
-  if (tiles >= sms) return 1;
+  if (tiles >= sms || tiles * 8 > kMaxCounters) return 1;
   int64_t s = sms / tiles;
   if (s > k_blocks / 2) s = k_blocks / 2;
   if (s > 16) s = 16;
   return s < 1 ? 1 : (int)s;
+}
+
+static __device__ __align__(256) unsigned int g_arrival_counters[kCounterRing];
+
+// This launch's `count` counters: the device address of the ring (looked up once per device, with that device
+// current: in host code the array's name is only a handle for the runtime) plus the next free segment.
+static int counter_segment(int count, unsigned int** out) {
+  static unsigned int* base[kMaxDevices] = {};
+  static unsigned int next[kMaxDevices] = {};
+  static std::mutex mu;
+  const int dev = device_slot();
+  if (dev < 0) return WUSH_ERR_BAD_SHAPE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_arrival_counters);
+    if (e != cudaSuccess) return (int)e;
+    base[dev] = static_cast<unsigned int*>(p);
+  }
+  if (next[dev] + (unsigned)count > (unsigned)kCounterRing) next[dev] = 0;
+  *out = base[dev] + next[dev];
+  next[dev] += (unsigned)count;
+  return WUSH_OK;
+}
+
+// After a launch that gave up on a wait the counters it touched may be non-zero: clear the ring (stream order).
+int reset_arrival_counters(cudaStream_t stream) {
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_arrival_counters);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p, 0, sizeof(unsigned int) * kCounterRing, stream);
+  return (int)e;
 }
 
 struct Shard {               // column-sharded output: where this GPU's columns go, here and on the other GPUs
@@ -780,21 +895,73 @@ struct Shard {               // column-sharded output: where this GPU's columns 
   int64_t ldy = 0, col0 = 0;
 };
 
+struct Epilogue {            // optional terms added to the output, and its row stride
+  const void* bias = nullptr;
+  const void* residual = nullptr;
+  int64_t ldr = 0;
+  int64_t ldy = 0;           // 0: n
+};
+
+// Tensor maps are pure functions of (base pointer, shape, box), and encoding one costs about a microsecond
+// of host time; a decode-size GEMM runs for a few microseconds.  The last maps are kept in a small
+// direct-mapped cache guarded by a mutex.
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+static int cached_operand_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_bytes, uint32_t box_rows) {
+  constexpr int kSlots = 64;
+  static MapKey keys[kSlots];
+  static CUtensorMap maps[kSlots];
+  static bool used[kSlots];
+  static std::mutex mu;
+  const MapKey key{base, rows, k_bytes, box_rows};
+  const size_t hsh = ((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull ^ (rows * 31 + k_bytes * 131 + box_rows);
+  const int slot = (int)((hsh >> 20) % kSlots);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (used[slot] && keys[slot] == key) {
+      *out = maps[slot];
+      return 0;
+    }
+  }
+  const int rc = make_tensor_map_2d(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, rows, k_bytes, k_bytes, BK / 2, box_rows,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != 0) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  keys[slot] = key;
+  maps[slot] = *out;
+  used[slot] = true;
+  return 0;
+}
+
 static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
-                       const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
-                       size_t workspace_bytes, int force_splits, int* status, cudaStream_t stream,
-                       const Shard* shard = nullptr) {
+                       const float* alpha, void* y, int64_t m, int64_t n, int64_t k, float* partial,
+                       size_t partial_bytes, int force_splits, int* status, cudaStream_t stream,
+                       const Shard* shard = nullptr, const Epilogue* epi = nullptr) {
   if (!a || !b || !sfa || !sfb || !alpha || !y) return WUSH_ERR_NULL_POINTER;
   if (m < 0 || n <= 0 || k <= 0 || k % 128 != 0 || n % 8 != 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
     return WUSH_ERR_BAD_SHAPE;
   if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)sfa & 15) || ((uintptr_t)sfb & 15) || ((uintptr_t)y & 15))
     return WUSH_ERR_BAD_ALIGNMENT;
   if (m == 0) return WUSH_OK;
+  int rc = require_sm100();
+  if (rc != 0) return rc;
   const int group = nv ? 16 : 32;
   Params p{};
   p.sfa = sfa; p.sfb = sfb; p.alpha = alpha; p.y = (__nv_bfloat16*)y;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.ldy = n;
+  if (epi) {
+    if (epi->ldy) p.ldy = epi->ldy;
+    p.bias = (const __nv_bfloat16*)epi->bias;
+    p.residual = (const __nv_bfloat16*)epi->residual;
+    p.ldr = epi->ldr ? epi->ldr : n;
+    if (p.ldy < n || p.ldy % 8 || p.ldr < n || p.ldr % 8) return WUSH_ERR_BAD_SHAPE;
+    if (((uintptr_t)p.bias & 15) || ((uintptr_t)p.residual & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  }
   if (shard) {
     p.ldy = shard->ldy;
     p.ycol0 = shard->col0;
@@ -814,36 +981,35 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   int splits = force_splits > 0 ? force_splits : choose_splits(tiles, p.k_blocks, sms);
   if (splits > p.k_blocks) splits = p.k_blocks;
   const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
-  if (need > workspace_bytes || (need && !workspace)) {
-    if (force_splits > 0) return WUSH_ERR_WORKSPACE_TOO_SMALL;
+  if (need > partial_bytes || (need && !partial) || (splits > 1 && tiles * 8 > kMaxCounters)) {
+    if (force_splits > 0) return tiles * 8 > kMaxCounters ? WUSH_ERR_TOO_LARGE : WUSH_ERR_WORKSPACE_TOO_SMALL;
     splits = 1;   // no room for partial tiles: run unsplit
   }
-  if (splits > 1 && ((uintptr_t)workspace & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (splits > 1 && ((uintptr_t)partial & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   p.splits = splits;
-  p.partial = (float*)workspace;
+  p.partial = partial;
+  if (splits > 1) {
+    rc = counter_segment((int)tiles * 8, &p.counters);
+    if (rc != 0) return rc;
+  }
 
   CUtensorMap amap, bmap;
-  int rc = make_tensor_map_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)m, (uint64_t)k / 2, (uint64_t)k / 2,
-                              BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != 0) return rc;
-  rc = make_tensor_map_2d(&bmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
-                          BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = cached_operand_map(&amap, a, (uint64_t)m, (uint64_t)k / 2, BM);
   if (rc != 0) return rc;
 
   // large M, unsplit: 256 x 256 tiles on CTA pairs
   static const int use_pair = env_int("WUSH_B200_GEMM_PAIR", 1);
   if (use_pair && splits == 1 && m > 128 && sms >= 2) {
-    CUtensorMap bmap2;
-    rc = make_tensor_map_2d(&bmap2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2,
-                            BK / 2, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = cached_operand_map(&bmap, b, (uint64_t)n, (uint64_t)k / 2, 128);
     if (rc != 0) return rc;
     auto pk = nv ? fp4_gemm_pair_kernel<true> : fp4_gemm_pair_kernel<false>;
     const int psmem = nv ? PairGeom<true>::SMEM : PairGeom<false>::SMEM;
-    static bool pair_attr_set[2] = {false, false};
-    static int max_pairs[2] = {0, 0};
-    if (!pair_attr_set[nv]) {
-      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem);
-      if (e != cudaSuccess) return (int)e;
+    static PerDevice pair_attr[2], max_pairs[2];
+    rc = opt_in_smem(pair_attr[nv], pk, psmem);
+    if (rc != 0) return rc;
+    const int dev = device_slot();
+    int nmax = dev >= 0 ? max_pairs[nv].get(dev) : 0;
+    if (nmax == 0) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * (sms / 2));
       cfg.blockDim = dim3(THREADS);
@@ -855,38 +1021,33 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
       attr.val.clusterDim.z = 1;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
-      int nmax = 0;
       if (cudaOccupancyMaxActiveClusters(&nmax, pk, &cfg) != cudaSuccess || nmax <= 0) nmax = sms / 2;
-      max_pairs[nv] = nmax;
-      pair_attr_set[nv] = true;
+      if (dev >= 0) max_pairs[nv].set(dev, nmax);
     }
     const int64_t ptiles = ((m + 255) / 256) * (int64_t)p.n_blocks;
-    int64_t pairs = max_pairs[nv] < sms / 2 ? max_pairs[nv] : sms / 2;
+    int64_t pairs = nmax < sms / 2 ? nmax : sms / 2;
     if (pairs > ptiles) pairs = ptiles;
-    pk<<<(unsigned)(2 * pairs), THREADS, psmem, stream>>>(amap, bmap2, p);
+    pk<<<(unsigned)(2 * pairs), THREADS, psmem, stream>>>(amap, bmap, p);
     return (int)cudaGetLastError();
   }
 
+  rc = cached_operand_map(&bmap, b, (uint64_t)n, (uint64_t)k / 2, BN);
+  if (rc != 0) return rc;
   auto kern = nv ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[nv]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set[nv] = true;
-  }
+  static PerDevice attr_one[2];
+  rc = opt_in_smem(attr_one[nv], kern, SMEM_BYTES);
+  if (rc != 0) return rc;
   int64_t work = tiles * splits;
   int grid = (int)(work < sms ? work : sms);
   kern<<<grid, THREADS, SMEM_BYTES, stream>>>(amap, bmap, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  if (splits > 1) {
-    const int64_t mn = m * n;   // n % 8 == 0, so rows stay 16-byte aligned and mn % 4 == 0
-    int64_t blocks = (mn / 4 + 255) / 256;
-    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partial, alpha, p.y, mn, splits);   // ldy == n here
-    e = cudaGetLastError();
-  }
-  return (int)e;
+  return (int)cudaGetLastError();
+}
+
+static int gemm_with_workspace(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                               const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
+                               size_t workspace_bytes, int splits, int* status, void* stream, const Epilogue* epi) {
+  return gemm_launch(nv, a, b, sfa, sfb, alpha, y, m, n, k, static_cast<float*>(workspace), workspace ? workspace_bytes : 0,
+                     splits, status, (cudaStream_t)stream, nullptr, epi);
 }
 
 }  // namespace gemm
@@ -895,15 +1056,27 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
 extern "C" int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                       const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
                                       size_t workspace_bytes, int splits, int* status, void* stream) {
-  return wush::gemm::gemm_launch(false, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
-                                 (cudaStream_t)stream);
+  return wush::gemm::gemm_with_workspace(false, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits,
+                                         status, stream, nullptr);
 }
 
 extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                       const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
                                       size_t workspace_bytes, int splits, int* status, void* stream) {
-  return wush::gemm::gemm_launch(true, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits, status,
-                                 (cudaStream_t)stream);
+  return wush::gemm::gemm_with_workspace(true, a, b, sfa, sfb, alpha, y, m, n, k, workspace, workspace_bytes, splits,
+                                         status, stream, nullptr);
+}
+
+extern "C" int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
+                                           const uint8_t* sfb, const float* alpha, const void* bias,
+                                           const void* residual, int64_t ldr, void* y, int64_t ldy, int64_t m,
+                                           int64_t n, int64_t k, void* workspace, size_t workspace_bytes, int splits,
+                                           int* status, void* stream) {
+  if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
+  wush::gemm::Epilogue epi;
+  epi.bias = bias; epi.residual = residual; epi.ldr = ldr; epi.ldy = ldy;
+  return wush::gemm::gemm_with_workspace(format == WUSH_FORMAT_NVFP4, a, b, sfa, sfb, alpha, y, m, n, k, workspace,
+                                         workspace_bytes, splits, status, stream, &epi);
 }
 
 extern "C" int wush_gemm_fp4_bf16_tn_sharded(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
@@ -939,17 +1112,18 @@ static __device__ __align__(256) float g_splitk_scratch[kStaticScratchFloats];
 // handle for the runtime, never a pointer a kernel could use, so the address is looked up once per
 // device (with that device current) and cached.
 static int static_scratch_address(float** out) {
-  constexpr int kMaxDevices = 64;
   static float* cache[kMaxDevices] = {};
   static std::mutex mu;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDevices) return WUSH_ERR_BAD_SHAPE;
+  const int dev = device_slot();
+  if (dev < 0) {
+    int d = 0;
+    const cudaError_t e = cudaGetDevice(&d);
+    return e != cudaSuccess ? (int)e : WUSH_ERR_BAD_SHAPE;
+  }
   std::lock_guard<std::mutex> lock(mu);
   if (!cache[dev]) {
     void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_splitk_scratch);
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_splitk_scratch);
     if (e != cudaSuccess) return (int)e;
     cache[dev] = static_cast<float*>(p);
   }
@@ -967,15 +1141,15 @@ extern "C" int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b
   if (m < 0 || n <= 0 || k <= 0) return WUSH_ERR_BAD_SHAPE;
   if (splits < 0) return WUSH_ERR_BAD_FLAG;
   const int k_blocks = (int)((k + BK - 1) / BK);
+  const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   if (splits == 0) {
-    const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     splits = choose_splits(tiles, k_blocks, wush::sm_count());
     // keep the partial tiles inside the fixed array, but stay a split-K launch
     while (splits > 2 && (size_t)splits * m * n > kStaticScratchFloats) --splits;
     if (splits < 2) splits = 2;
   }
   if (splits < 2 || splits > k_blocks) return WUSH_ERR_BAD_FLAG;   // K too short to split, or a forced value out of range
-  if ((size_t)splits * (size_t)m * (size_t)n > kStaticScratchFloats) return WUSH_ERR_TOO_LARGE;
+  if ((size_t)splits * (size_t)m * (size_t)n > kStaticScratchFloats || tiles * 8 > kMaxCounters) return WUSH_ERR_TOO_LARGE;
   float* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != WUSH_OK) return rc;

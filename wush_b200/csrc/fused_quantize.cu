@@ -461,18 +461,16 @@ static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   dim3 grid((unsigned)slabs, (unsigned)splits);
   auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL>;
   constexpr int smem = kQuantSmem;
-  static bool attr_set = false;  // per instantiation; the attribute is per function and idempotent
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
+  static PerDevice attr_set;     // per instantiation and device
+  const int rc = opt_in_smem(attr_set, kern, smem);
+  if (rc != 0) return rc;
   kern<<<grid, kWarps * 32, smem, stream>>>(p);
   return (int)cudaGetLastError();
 }
 
 template <bool NV, bool DEBUG>
 static int launch_quant(const QuantParams& p, cudaStream_t stream) {
+  if (const int rc100 = require_sm100()) return rc100;
   const bool rb = p.round_bf16 != 0, bl = p.sf_layout == WUSH_SF_BLOCKED;
   if (rb) return bl ? launch_quant_t<NV, DEBUG, true, true>(p, stream) : launch_quant_t<NV, DEBUG, true, false>(p, stream);
   return bl ? launch_quant_t<NV, DEBUG, false, true>(p, stream) : launch_quant_t<NV, DEBUG, false, false>(p, stream);

@@ -14,6 +14,7 @@
 #include <stdint.h>
 
 #include "../../include/wush_b200.h"
+#include "common.cuh"
 
 namespace wush {
 namespace sweep {
@@ -458,6 +459,7 @@ extern "C" WUSH_API int wush_gptq_block_step(const double* rn, const double* yne
     return WUSH_ERR_BAD_SHAPE;
   if (nblocks > 65535) return WUSH_ERR_TOO_LARGE;
   if ((reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(fake)) & 15) return WUSH_ERR_BAD_ALIGNMENT;
+  if (const int rc100 = wush::require_sm100()) return rc100;
   if (rows == 0 || nblocks == 0) return WUSH_OK;
   Params p{rn, ynew, qt, tmat, codes, scales, fake, coef, rows, cols, col_block0, (flags & WUSH_SWEEP_RTN_ONLY) != 0,
            (flags & WUSH_SWEEP_FAKE_F32) != 0};
@@ -478,6 +480,7 @@ extern "C" WUSH_API int wush_gptq_block_prepare(const double* gram, const double
   if (flags & ~WUSH_SWEEP_FAKE_F32) return WUSH_ERR_BAD_FLAG;
   const int g = format == WUSH_FORMAT_NVFP4 ? 16 : 32;
   if (nblocks < 0 || ldb < g || rows <= 0) return WUSH_ERR_BAD_SHAPE;
+  if (const int rc100 = wush::require_sm100()) return rc100;
   if (nblocks == 0) return WUSH_OK;
   PrepParams p{gram, basis, ldb, basis_step, tmat, rn, qt, transform, (flags & WUSH_SWEEP_FAKE_F32) != 0,
                1.0 / sqrt((double)rows), status};

@@ -27,6 +27,7 @@
 
 #include "../../include/wush_b200.h"
 #include "common.cuh"
+#include "hess_tiles.cuh"
 #include "sm100.cuh"
 
 namespace wush {
@@ -72,6 +73,8 @@ struct Params {
   int last_block;
   int ksplit;       // CTAs sharing the token range of one tile (> 1: results are added with atomics)
   int lower_only;   // do not mirror into the upper triangle
+  int overwrite;    // H = X^T X: the previous contents are not read (ksplit == 1 only)
+  int tile_off;     // CTA-pair kernel: first entry of the tile list handled by this launch
   int* status;      // optional device word, set to 1 when a bounded wait ran out
 };
 
@@ -137,7 +140,8 @@ __device__ __forceinline__ void update_h(const Params& p, float (&acc)[128], int
       // chunk entirely in the lower triangle of this row (and inside the matrix)
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        float4 o = *reinterpret_cast<const float4*>(hrow + jc + 4 * u);
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!p.overwrite) o = *reinterpret_cast<const float4*>(hrow + jc + 4 * u);
         o.x += acc[c * 32 + 4 * u];
         o.y += acc[c * 32 + 4 * u + 1];
         o.z += acc[c * 32 + 4 * u + 2];
@@ -150,7 +154,7 @@ __device__ __forceinline__ void update_h(const Params& p, float (&acc)[128], int
 #pragma unroll
       for (int u = 0; u < 32; ++u) {
         if (row_ok && jc + u <= i) {
-          acc[c * 32 + u] += hrow[jc + u];
+          if (!p.overwrite) acc[c * 32 + u] += hrow[jc + u];
           hrow[jc + u] = acc[c * 32 + u];
         }
       }
@@ -332,28 +336,6 @@ __global__ void __launch_bounds__(THREADS, 1) hessian_kernel(const __grid_consta
 constexpr int P_STAGES = 6;
 constexpr int P_STAGE_BYTES = A_BYTES + B_BYTES / 2;   // 32 KB per CTA: 128 rows of A, 128 columns of B
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
-constexpr int P_BAND = 8;                              // row blocks (of 256) per band of the tile order
-
-// pair tile t -> (row block bi2, column block bj2 <= bi2) in units of 256, banded like tile_coords
-__device__ __forceinline__ void pair_tile_coords(int t, int first_block, int last_block, int& bi, int& bj) {
-  for (int lo = first_block;; lo += P_BAND) {
-    const int hi = min(lo + P_BAND, last_block);
-    for (int c = 0; c < hi; ++c) {
-      const int first = max(lo, c);
-      const int cnt = hi - first;
-      if (t < cnt) {
-        bi = first + t;
-        bj = c;
-        return;
-      }
-      t -= cnt;
-    }
-    if (hi >= last_block) break;
-  }
-  bi = first_block;
-  bj = 0;
-}
-
 template <bool F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
@@ -412,7 +394,7 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
       for (int w = pair_id; w < n_work && ok; w += n_pairs) {
         int t, kbeg, kend, bi, bj;
         work_range(p, w, k_blocks, t, kbeg, kend);
-        pair_tile_coords(t, p.first_block, p.last_block, bi, bj);
+        pair_tile_coords(t + p.tile_off, p.first_block, p.last_block, bi, bj);
         const int a_col = bi * 256 + (int)rank * 128, b_col = bj * 256 + (int)rank * 128;
         for (int kb = kbeg; kb < kend; ++kb) {
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
@@ -470,7 +452,7 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
     for (int w = pair_id; w < n_work && ok; w += n_pairs) {
       int t, kbeg, kend, bi, bj;
       work_range(p, w, k_blocks, t, kbeg, kend);
-      pair_tile_coords(t, p.first_block, p.last_block, bi, bj);
+      pair_tile_coords(t + p.tile_off, p.first_block, p.last_block, bi, bj);
       float acc[128];
 #pragma unroll
       for (int u = 0; u < 128; ++u) acc[u] = 0.0f;
@@ -518,69 +500,122 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap xmap, const Params p) {
 
 using namespace wush;
 
+// tile_begin < 0: rows [row_begin, row_end) of H; otherwise entries [tile_begin, tile_end) of the 256 x 256 tile list
 static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
-                              int64_t row_end, int flags, int* status, cudaStream_t stream);
+                              int64_t row_end, int64_t tile_begin, int64_t tile_end, int flags, int* status,
+                              cudaStream_t stream);
 
 // Tokens per kernel launch.  The CTAs of a launch walk the token axis side by side and share the X
 // blocks they read through L2; over very long token ranges they drift apart and that sharing is lost
 // (measured at hidden 14336: 1230 TFLOP/s with 32768 tokens per launch, 800 with 262144), so long
 // inputs are cut into segments.  Earlier segments only update the lower triangle; the mirror image is
-// written once, by the last segment.
+// written once, by the last segment.  Only the first segment may overwrite.
 constexpr int64_t kSegmentTokens = 32768;
 
 static int hessian_launch(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin, int64_t row_end,
-                          int flags, int* status, cudaStream_t stream) {
-  if (tokens <= kSegmentTokens + kSegmentTokens / 2)
-    return hessian_launch_one(h, x, tokens, hidden, row_begin, row_end, flags, status, stream);
-  if (!x || hidden <= 0) return hessian_launch_one(h, x, tokens, hidden, row_begin, row_end, flags, status, stream);
+                          int64_t tile_begin, int64_t tile_end, int flags, int* status, cudaStream_t stream) {
+  if (tokens <= kSegmentTokens + kSegmentTokens / 2 || !x || hidden <= 0)
+    return hessian_launch_one(h, x, tokens, hidden, row_begin, row_end, tile_begin, tile_end, flags, status, stream);
   const char* xb = static_cast<const char*>(x);
   for (int64_t t0 = 0; t0 < tokens; t0 += kSegmentTokens) {
     const int64_t n = tokens - t0 < kSegmentTokens + kSegmentTokens / 2 ? tokens - t0 : kSegmentTokens;
     const bool last = t0 + n >= tokens;
-    const int rc = hessian_launch_one(h, xb + t0 * hidden * ((flags & WUSH_HESSIAN_INPUT_F32) ? 4 : 2), n, hidden, row_begin, row_end,
-                                      last ? flags : (flags | WUSH_HESSIAN_LOWER_ONLY), status, stream);
+    int f = last ? flags : (flags | WUSH_HESSIAN_LOWER_ONLY);
+    if (t0 > 0) f &= ~WUSH_HESSIAN_OVERWRITE;
+    const int rc = hessian_launch_one(h, xb + t0 * hidden * ((flags & WUSH_HESSIAN_INPUT_F32) ? 4 : 2), n, hidden, row_begin,
+                                      row_end, tile_begin, tile_end, f, status, stream);
     if (rc != 0) return rc;
     if (last) break;
   }
   return 0;
 }
 
+// CTA pairs (clusters of 2) that can be resident at once on the current device; SMs that cannot be paired
+// inside their GPC stay idle.  Cached per device.
+template <class Kernel>
+static int resident_pairs(PerDevice& cache, Kernel pk, int threads, int smem, int units) {
+  const int dev = device_slot();
+  if (dev >= 0 && cache.get(dev)) return cache.get(dev);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * units);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, pk, &cfg) != cudaSuccess || n <= 0) n = units;
+  if (n > units) n = units;
+  if (dev >= 0) cache.set(dev, n);
+  return n;
+}
+
+static int hessian_pairs_on_device() {
+  static PerDevice attr, pairs;
+  auto pk = hess::hessian_pair_kernel<false>;
+  if (opt_in_smem(attr, pk, hess::P_SMEM_BYTES) != 0) return 0;
+  const int sms = sm_count();
+  return sms < 2 ? 0 : resident_pairs(pairs, pk, hess::THREADS, hess::P_SMEM_BYTES, sms / 2);
+}
+
 static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
-                              int64_t row_end, int flags, int* status, cudaStream_t stream) {
+                              int64_t row_end, int64_t tile_begin, int64_t tile_end, int flags, int* status,
+                              cudaStream_t stream) {
   if (!h || !x) return WUSH_ERR_NULL_POINTER;
   if (tokens < 0 || hidden <= 0 || hidden % 8 != 0 || tokens > 0x7fffffff || hidden > (1 << 20)) return WUSH_ERR_BAD_SHAPE;
-  if (row_begin < 0 || row_end > hidden || row_begin > row_end || row_begin % hess::BM != 0 ||
-      (row_end % hess::BM != 0 && row_end != hidden))
+  const bool by_tiles = tile_begin >= 0;
+  const int64_t nblk256 = (hidden + 255) / 256;
+  if (by_tiles) {
+    if (tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk256)) return WUSH_ERR_BAD_SHAPE;
+  } else if (row_begin < 0 || row_end > hidden || row_begin > row_end || row_begin % hess::BM != 0 ||
+             (row_end % hess::BM != 0 && row_end != hidden)) {
     return WUSH_ERR_BAD_SHAPE;
-  if (flags & ~(WUSH_HESSIAN_LOWER_ONLY | WUSH_HESSIAN_INPUT_F32)) return WUSH_ERR_BAD_FLAG;
+  }
+  if (flags & ~(WUSH_HESSIAN_LOWER_ONLY | WUSH_HESSIAN_INPUT_F32 | WUSH_HESSIAN_OVERWRITE)) return WUSH_ERR_BAD_FLAG;
   const bool f32 = (flags & WUSH_HESSIAN_INPUT_F32) != 0;
   if (((uintptr_t)h & 15) || ((uintptr_t)x & 15)) return WUSH_ERR_BAD_ALIGNMENT;
-  if (tokens == 0 || row_begin == row_end) return WUSH_OK;
+  if (tokens == 0 || (by_tiles ? tile_begin == tile_end : row_begin == row_end)) return WUSH_OK;
+  int rc = require_sm100();
+  if (rc != 0) return rc;
 
   CUtensorMap map;
-  int rc = f32 ? make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, (uint64_t)tokens, (uint64_t)hidden,
-                                    (uint64_t)hidden * 4, hess::Elem<true>::BOXC, hess::Elem<true>::KT,
-                                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
-               : make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
-                                    (uint64_t)hidden * 2, hess::Elem<false>::BOXC, hess::Elem<false>::KT,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = f32 ? make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, (uint64_t)tokens, (uint64_t)hidden,
+                                (uint64_t)hidden * 4, hess::Elem<true>::BOXC, hess::Elem<true>::KT,
+                                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
+           : make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)tokens, (uint64_t)hidden,
+                                (uint64_t)hidden * 2, hess::Elem<false>::BOXC, hess::Elem<false>::KT,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != 0) return rc;
 
   const int sms = sm_count();
   // CTA-pair kernel: 256 x 256 tiles, needs row panels aligned to 256 and at least one pair of SMs
   static const int use_pair = env_int("WUSH_B200_HESSIAN_PAIR", 1);
-  const bool pair = use_pair && row_begin % 256 == 0 && (row_end % 256 == 0 || row_end == hidden) && sms >= 2;
+  const bool pair = by_tiles || (use_pair && row_begin % 256 == 0 && (row_end % 256 == 0 || row_end == hidden) && sms >= 2);
+  if (pair && sms < 2) return WUSH_ERR_BAD_FLAG;
   const int blk = pair ? 256 : hess::BM;
-  const int b0 = (int)(row_begin / blk), b1 = (int)((row_end + blk - 1) / blk);
+  int b0, b1;
   int64_t n_tiles = 0;
-  for (int b = b0; b < b1; ++b) n_tiles += pair ? b + 1 : (b >> 1) + 1;
-  // column blocks past the matrix edge never exist: they start at or before their row block
+  if (by_tiles) {
+    b0 = 0;
+    b1 = (int)nblk256;
+    n_tiles = tile_end - tile_begin;
+  } else {
+    b0 = (int)(row_begin / blk);
+    b1 = (int)((row_end + blk - 1) / blk);
+    // column blocks past the matrix edge never exist: they start at or before their row block
+    for (int b = b0; b < b1; ++b) n_tiles += pair ? b + 1 : (b >> 1) + 1;
+  }
   const int units = pair ? sms / 2 : sms;   // CTAs (or CTA pairs) working side by side
 
-  // Token splits: only in lower-only mode (the mirror needs final values).  Pick the split count that
-  // wastes the least of the last wave, keeping at least 1024 tokens per split.
+  // Token splits: only in lower-only mode (the mirror needs final values) and not when overwriting (the
+  // splits add into H with atomics).  Pick the split count that wastes the least of the last wave, keeping
+  // at least 1024 tokens per split.
   int ksplit = 1;
-  if (flags & WUSH_HESSIAN_LOWER_ONLY) {
+  if ((flags & WUSH_HESSIAN_LOWER_ONLY) && !(flags & WUSH_HESSIAN_OVERWRITE)) {
     const int max_split = (int)(tokens / 1024 < 1 ? 1 : (tokens / 1024 > 16 ? 16 : tokens / 1024));
     double best = 1e30;
     for (int ks = 1; ks <= max_split; ++ks) {
@@ -589,47 +624,25 @@ static int hessian_launch_one(float* h, const void* x, int64_t tokens, int64_t h
       if (cost < best - 1e-9) { best = cost; ksplit = ks; }
     }
   }
-  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, b1, ksplit, (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, status};
+  hess::Params p{h, hidden, (int)hidden, (int)tokens, (int)n_tiles, b0, b1, ksplit,
+                 (flags & WUSH_HESSIAN_LOWER_ONLY) ? 1 : 0, (flags & WUSH_HESSIAN_OVERWRITE) ? 1 : 0,
+                 by_tiles ? (int)tile_begin : 0, status};
 
   if (pair) {
     auto pk = f32 ? hess::hessian_pair_kernel<true> : hess::hessian_pair_kernel<false>;
-    static bool attr_set_pair[2] = {false, false};
-    if (!attr_set_pair[f32]) {
-      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, hess::P_SMEM_BYTES);
-      if (e != cudaSuccess) return (int)e;
-      attr_set_pair[f32] = true;
-    }
-    // clusters of 2 that can be resident at once (SMs that cannot be paired inside their GPC stay idle)
-    static int max_pairs = 0;
-    if (max_pairs == 0) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(2 * units);
-      cfg.blockDim = dim3(hess::THREADS);
-      cfg.dynamicSmemBytes = hess::P_SMEM_BYTES;
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2;
-      attr.val.clusterDim.y = 1;
-      attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, pk, &cfg) != cudaSuccess || n <= 0) n = units;
-      max_pairs = n;
-    }
-    int64_t pairs = max_pairs < units ? max_pairs : units;
+    static PerDevice attr_pair[2], max_pairs[2];
+    rc = opt_in_smem(attr_pair[f32], pk, hess::P_SMEM_BYTES);
+    if (rc != 0) return rc;
+    int64_t pairs = resident_pairs(max_pairs[f32], pk, hess::THREADS, hess::P_SMEM_BYTES, units);
     if (pairs > n_tiles * ksplit) pairs = n_tiles * ksplit;
     pk<<<(unsigned)(2 * pairs), hess::THREADS, hess::P_SMEM_BYTES, stream>>>(map, p);
     return (int)cudaGetLastError();
   }
 
   auto k1 = f32 ? hess::hessian_kernel<true> : hess::hessian_kernel<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[f32]) {
-    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, hess::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set[f32] = true;
-  }
+  static PerDevice attr_one[2];
+  rc = opt_in_smem(attr_one[f32], k1, hess::SMEM_BYTES);
+  if (rc != 0) return rc;
   int grid = sms;
   if (grid > n_tiles * ksplit) grid = (int)(n_tiles * ksplit);
   k1<<<grid, hess::THREADS, hess::SMEM_BYTES, stream>>>(map, p);
@@ -640,11 +653,13 @@ namespace wush {
 namespace hess {
 // Lower triangle (already summed) -> scaled lower triangle and its mirror image, 32 x 32 tiles:
 // a block reads tile (bi, bj), bj <= bi, scales it in place and writes its transpose to (bj, bi)
-// through shared memory, so both the reads and the mirrored writes are coalesced.
+// through shared memory, so both the reads and the mirrored writes are coalesced.  With scale == 1
+// the lower triangle is left alone (mirror only).
 __global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float scale, const long long* __restrict__ count,
                                 int64_t tiles_per_side) {
   __shared__ float tile[32][33];
   if (count) scale = 1.0f / (float)(*count > 0 ? *count : 1);   // token count produced on the device (all-reduce)
+  const bool rescale = scale != 1.0f;
   const int64_t n_tiles = tiles_per_side * (tiles_per_side + 1) / 2;
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     // t -> (bi, bj) with bj <= bi
@@ -659,7 +674,7 @@ __global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float sca
       float v = 0.0f;
       if (i < hidden && j < hidden && j <= i) {
         v = h[i * hidden + j] * scale;
-        h[i * hidden + j] = v;
+        if (rescale) h[i * hidden + j] = v;
       }
       tile[r][tx] = v;
     }
@@ -673,17 +688,77 @@ __global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float sca
     __syncthreads();
   }
 }
+
+// Mirror image of entries [tile_begin, tile_end) of the 256 x 256 tile list: a block copies one 32 x 32
+// sub-tile of the lower triangle to its transposed place.  Sub-tiles above the diagonal of a diagonal tile
+// are skipped, diagonal sub-tiles mirror their strictly lower part.
+__global__ void mirror_tiles_kernel(float* __restrict__ h, int64_t hidden, int nblk, int64_t tile_begin, int64_t n_items) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int64_t k = blockIdx.x; k < n_items; k += gridDim.x) {
+    int bi, bj;
+    pair_tile_coords(tile_begin + (k >> 6), 0, nblk, bi, bj);
+    const int sub = (int)(k & 63);
+    const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);   // 32 x 32 sub-tile (si, sj)
+    if (sj > si) continue;                                                             // uniform per block
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t i = si * 32 + r, j = sj * 32 + tx;
+      tile[r][tx] = (i < hidden && j < hidden && j <= i) ? h[i * hidden + j] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t jr = sj * 32 + r, ic = si * 32 + tx;
+      if (jr < hidden && ic < hidden && jr < ic) h[jr * hidden + ic] = tile[tx][r];
+    }
+    __syncthreads();
+  }
+}
 }  // namespace hess
 }  // namespace wush
 
 extern "C" int wush_hessian_accumulate(float* h, const void* x, int64_t tokens, int64_t hidden, int flags, int* status,
                                        void* stream) {
-  return hessian_launch(h, x, tokens, hidden, 0, hidden, flags, status, (cudaStream_t)stream);
+  return hessian_launch(h, x, tokens, hidden, 0, hidden, -1, -1, flags, status, (cudaStream_t)stream);
 }
 
 extern "C" int wush_hessian_accumulate_rows(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t row_begin,
                                             int64_t row_end, int flags, int* status, void* stream) {
-  return hessian_launch(h, x, tokens, hidden, row_begin, row_end, flags, status, (cudaStream_t)stream);
+  return hessian_launch(h, x, tokens, hidden, row_begin, row_end, -1, -1, flags, status, (cudaStream_t)stream);
+}
+
+extern "C" int64_t wush_hessian_tile_count(int64_t hidden) {
+  return hidden <= 0 ? 0 : hess::pair_tile_count((hidden + 255) / 256);
+}
+
+extern "C" int wush_hessian_tiles_per_wave(void) { return hessian_pairs_on_device(); }
+
+extern "C" int wush_hessian_tile_coords(int64_t hidden, int64_t tile, int* row_block, int* col_block) {
+  if (!row_block || !col_block) return WUSH_ERR_NULL_POINTER;
+  if (hidden <= 0 || tile < 0 || tile >= wush_hessian_tile_count(hidden)) return WUSH_ERR_BAD_SHAPE;
+  hess::pair_tile_coords(tile, 0, (int)((hidden + 255) / 256), *row_block, *col_block);
+  return WUSH_OK;
+}
+
+extern "C" int wush_hessian_accumulate_tiles(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t tile_begin,
+                                             int64_t tile_end, int flags, int* status, void* stream) {
+  if (tile_begin < 0) return WUSH_ERR_BAD_SHAPE;
+  return hessian_launch(h, x, tokens, hidden, 0, hidden, tile_begin, tile_end, flags, status, (cudaStream_t)stream);
+}
+
+extern "C" int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream) {
+  if (!h) return WUSH_ERR_NULL_POINTER;
+  if (hidden <= 0 || tile_begin < 0 || tile_end < tile_begin || tile_end > wush_hessian_tile_count(hidden))
+    return WUSH_ERR_BAD_SHAPE;
+  const int64_t items = (tile_end - tile_begin) * 64;
+  if (items == 0) return WUSH_OK;
+  int64_t blocks = items;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  hess::mirror_tiles_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, (int)((hidden + 255) / 256),
+                                                                               tile_begin, items);
+  return (int)cudaGetLastError();
 }
 
 static int hessian_finalize(float* h, int64_t hidden, float scale, const long long* count, void* stream);

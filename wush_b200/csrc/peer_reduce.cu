@@ -1,20 +1,29 @@
-// Cross-GPU sum of the Hessian over NVLink peer memory, fused with the 1/N scaling and the mirror.
+// Cross-GPU sum of the Hessian over NVLink, fused with the 1/N scaling.
 //
-// Every rank holds its raw lower-triangle sum in a buffer that all ranks can address (symmetric
-// memory, one process per GPU).  The lower triangle is cut into 32 x 32 tiles dealt round-robin to the
-// ranks.  For each tile it owns, a rank reads the tile from every rank's buffer with plain peer loads,
-// adds them (a tile is summed by its owner alone, so all ranks end up with bit-identical results), scales by 1 / total
-// tokens, and stores the finished tile and its mirror image into every rank's buffer with peer stores.
-// A given tile of any buffer is only ever touched by its owner's kernel, so the exchange can run in
-// place; the caller brackets the launch with two cross-rank barriers (all partial sums complete before
-// / all results delivered after).  One kernel replaces an all-reduce, a scaling pass and a mirror pass;
-// per rank it moves (W-1)/W of the triangle in and twice that out over NVSwitch.
-// No TMA, no multicast: ordinary 16-byte loads and stores on peer pointers.
+// Every rank holds its raw lower-triangle sum in a buffer that all ranks can address (symmetric memory, one
+// process per GPU).  The kernel takes a range of the 256 x 256 tile list the accumulation kernel walks
+// (hess_tiles.cuh), cut into 32 x 32 sub-tiles that are dealt round-robin to the ranks.  For each sub-tile it
+// owns, a rank sums the sub-tile over all ranks, scales by 1 / total tokens and delivers the result to the
+// same place of every rank's buffer.  A sub-tile is summed by its owner alone, so all ranks end up with
+// bit-identical results, and a given sub-tile of any buffer is only ever touched by its owner's kernel, so
+// the exchange runs in place.  Two ways to move the data:
+//   plain      peer loads from every rank's buffer (starting with the own one, then round the ring), peer
+//              stores into every rank's buffer: (W-1)/W of the range in and out per rank;
+//   multimem   one multimem.ld_reduce per 16 bytes (the NVSwitch adds the W copies on the way) and one
+//              multimem.st (the switch replicates it): a rank pulls and pushes 1/W of the range, its links
+//              carry about half of what the plain exchange needs.
+// Only the lower triangle travels; every rank rebuilds the mirror image locally at HBM speed
+// (wush_hessian_mirror_tiles).  The caller brackets the launch with two cross-rank barriers (the partial sums
+// of the range are complete everywhere before / every rank has delivered after).  Because the kernel works
+// on tile ranges, finished ranges can be combined while the accumulation kernel is still busy with later
+// tiles: it is small enough (256 threads, 40 registers, 4 KB of shared memory) to be co-resident with it.
+// No TMA, no cluster multicast: 16-byte loads and stores on peer or multicast addresses.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/wush_b200.h"
 #include "common.cuh"
+#include "hess_tiles.cuh"
 
 namespace wush {
 namespace peer {
@@ -22,18 +31,36 @@ namespace peer {
 constexpr int kMaxWorld = 16;
 
 struct Params {
-  float* const* bufs;            // device array [world]: base of every rank's H buffer
+  float* const* bufs;              // device array [world]: base of every rank's H buffer
+  float* mc;                       // multicast address of the same buffer (multimem variant), else null
   const long long* const* counts;  // device array [world]: every rank's local token count
   int rank, world;
   int64_t hidden;
-  int64_t tiles_per_side;
+  int nblk;                        // row blocks of 256
+  int64_t tile_begin;
+  int64_t n_items;                 // (tiles in range) * (sub-tiles per tile owned by this rank)
+  int per_tile;                    // sub-tiles of one tile owned by this rank
 };
 
+__device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(float* mc_addr, const float4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"l"(mc_addr), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+template <bool MC>
 __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
-  __shared__ float tile[32][33];
   __shared__ float* s_bufs[kMaxWorld];
   __shared__ float s_scale;
-  if (threadIdx.x < p.world) s_bufs[threadIdx.x] = p.bufs[threadIdx.x];
+  if (threadIdx.x < p.world) s_bufs[threadIdx.x] = p.bufs[(threadIdx.x + p.rank) % p.world];   // own buffer first
   if (threadIdx.x == 0) {
     long long total = 0;
     for (int r = 0; r < p.world; ++r) total += *p.counts[r];
@@ -41,78 +68,62 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
   }
   __syncthreads();
   const float scale = s_scale;
-  const int64_t n_tiles = p.tiles_per_side * (p.tiles_per_side + 1) / 2;
-  const int row_in = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;   // this thread's float4 inside a tile
-  const bool vec_ok = (p.hidden & 3) == 0;
-  (void)vec_ok;
+  const int row_in = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;   // this thread's float4 inside a sub-tile
 
-  // tiles owned by this rank: t = rank, rank + world, ...; the CTAs of the grid share them
-  for (int64_t k = blockIdx.x;; k += gridDim.x) {
-    const int64_t t = (int64_t)p.rank + k * p.world;
-    if (t >= n_tiles) break;
-    int64_t bi = (int64_t)((sqrt(8.0 * (double)t + 1.0) - 1.0) * 0.5);
-    while (bi * (bi + 1) / 2 > t) --bi;
-    while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
-    const int64_t bj = t - bi * (bi + 1) / 2;
-    const int64_t i = bi * 32 + row_in, j = bj * 32 + c4;
-
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const bool in = i < p.hidden && j < p.hidden;     // hidden % 4 == 0: a float4 never straddles the edge
-    if (in) {
-      const int64_t off = i * p.hidden + j;
-      // start with the own buffer and walk the ring, so that the ranks do not all read from the same GPU at
-      // once; a tile is summed by its owner alone, so the order is a fixed function of the tile
+  for (int64_t k = blockIdx.x; k < p.n_items; k += gridDim.x) {
+    int bi, bj;
+    hess::pair_tile_coords(p.tile_begin + k / p.per_tile, 0, p.nblk, bi, bj);
+    const int sub = p.rank + (int)(k % p.per_tile) * p.world;          // sub-tile (sub / 8, sub % 8) of the tile
+    const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);
+    if (sj > si) continue;                                             // above the diagonal: nothing there
+    const int64_t i = si * 32 + row_in, j = sj * 32 + c4;
+    if (i >= p.hidden || j >= p.hidden) continue;                      // hidden % 4 == 0: a float4 never straddles the edge
+    const int64_t off = i * p.hidden + j;
+    float4 acc;
+    if (MC) {
+      acc = multimem_ld_reduce_add(p.mc + off);
+    } else {
+      // a sub-tile is summed by its owner alone, so the order is a fixed function of the sub-tile
+      acc = *reinterpret_cast<const float4*>(s_bufs[0] + off);
 #pragma unroll 8
-      for (int r = 0; r < p.world; ++r) {
-        const float4 v = *reinterpret_cast<const float4*>(s_bufs[(r + p.rank) % p.world] + off);
+      for (int r = 1; r < p.world; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(s_bufs[r] + off);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
-      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
     }
-    // entries above the diagonal of a diagonal tile are not part of the sums: take them from the mirror
-    tile[row_in][c4] = acc.x; tile[row_in][c4 + 1] = acc.y; tile[row_in][c4 + 2] = acc.z; tile[row_in][c4 + 3] = acc.w;
-    __syncthreads();
-    if (bi == bj) {
-      float* e = &acc.x;
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (c4 + u > row_in) e[u] = tile[c4 + u][row_in];
-    }
-    // transposed element block for the mirror tile: row (bj*32 + row_in), columns (bi*32 + c4 ..)
-    float4 tr;
-    if (bi == bj) {
-      tr = acc;   // the diagonal tile is its own mirror once completed
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    if (MC) {
+      multimem_st(p.mc + off, acc);
     } else {
-      tr = make_float4(tile[c4][row_in], tile[c4 + 1][row_in], tile[c4 + 2][row_in], tile[c4 + 3][row_in]);
+#pragma unroll 8
+      for (int r = 0; r < p.world; ++r) *reinterpret_cast<float4*>(s_bufs[r] + off) = acc;
     }
-    const int64_t mi = bj * 32 + row_in, mj = bi * 32 + c4;
-    const bool min_ok = mi < p.hidden && mj < p.hidden;
-#pragma unroll 4
-    for (int r = 0; r < p.world; ++r) {
-      float* dst = s_bufs[(r + p.rank) % p.world];    // start with the own buffer, spread the peers
-      if (in) *reinterpret_cast<float4*>(dst + i * p.hidden + j) = acc;
-      if (bi != bj && min_ok) *reinterpret_cast<float4*>(dst + mi * p.hidden + mj) = tr;
-    }
-    __syncthreads();
   }
 }
 
 }  // namespace peer
 }  // namespace wush
 
-extern "C" int wush_hessian_peer_reduce(float* const* bufs, const int64_t* const* counts, int rank, int world,
-                                        int64_t hidden, void* stream) {
+extern "C" int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const int64_t* const* counts, int rank,
+                                        int world, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream) {
   using namespace wush;
   if (!bufs || !counts) return WUSH_ERR_NULL_POINTER;
   if (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world) return WUSH_ERR_BAD_SHAPE;
   if (hidden <= 0 || hidden % 4 != 0) return WUSH_ERR_BAD_SHAPE;
-  peer::Params p{bufs, reinterpret_cast<const long long* const*>(counts), rank, world, hidden, (hidden + 31) / 32};
-  const int64_t n_tiles = p.tiles_per_side * (p.tiles_per_side + 1) / 2;
-  int64_t mine = (n_tiles - rank + world - 1) / world;
-  if (mine <= 0) return WUSH_OK;
-  int64_t blocks = mine;
+  const int nblk = (int)((hidden + 255) / 256);
+  if (tile_begin < 0 || tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk)) return WUSH_ERR_BAD_SHAPE;
+  if (mc_buf && ((uintptr_t)mc_buf & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  peer::Params p{bufs, mc_buf, reinterpret_cast<const long long* const*>(counts), rank, world, hidden, nblk,
+                 tile_begin, 0, 0};
+  p.per_tile = rank < 64 ? (64 - rank + world - 1) / world : 0;
+  p.n_items = (tile_end - tile_begin) * p.per_tile;
+  if (p.n_items <= 0) return WUSH_OK;
+  int64_t blocks = p.n_items;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  peer::peer_reduce_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  if (mc_buf)
+    peer::peer_reduce_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  else
+    peer::peer_reduce_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
   return (int)cudaGetLastError();
 }

@@ -37,6 +37,7 @@ extern "C" int wush_sf_to_blocked(const uint8_t* in, uint8_t* out, int64_t rows,
   const int64_t row_blocks = (rows + 127) / 128, col_blocks = (cols + 3) / 4;
   const int64_t words = row_blocks * col_blocks * 128;
   if (words == 0) return WUSH_OK;
+  if (const int rc100 = wush::require_sm100()) return rc100;
   const int threads = 256;
   int64_t blocks = (words + threads - 1) / threads;
   const int64_t cap = (int64_t)wush::sm_count() * 16;

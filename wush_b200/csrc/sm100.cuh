@@ -51,10 +51,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // seconds of wall time at most -- far beyond any legitimate wait in these kernels.
 constexpr uint32_t kMaxPolls = 1u << 22;
 
-// Returns false when the wait ran out or another thread of the CTA already raised `abort_flag`
-// (a word in shared memory); the caller unwinds instead of spinning on.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+// Returns false when the wait ran out (after `max_polls` polls) or another thread of the CTA already raised
+// `abort_flag` (a word in shared memory); the caller unwinds instead of spinning on.
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t max_polls) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63) == 63) {
       if (*abort_flag) return false;
@@ -63,6 +64,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kMaxPolls);
 }
 
 // ---- TMA -------------------------------------------------------------------------------------

@@ -101,3 +101,4 @@ class HostQuantizer:
 
     def synchronize(self) -> None:
         self.done.synchronize()
+        _lib.check_status(self.dev, "host-streamed quantize")

@@ -87,13 +87,20 @@ class FPQuantLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, **kw), requires_grad=False) if bias else None
         self.register_buffer("qweight", torch.empty(out_features, in_features // 2, dtype=torch.uint8, device=device))
         self.register_buffer("scales", torch.empty(out_features, in_features // g, dtype=torch.uint8, device=device))
-        gs = 3.0 if config.forward_dtype == FPQuantDtype.MXFP4 else 10.0    # linear.py:207-217, wush_gptq.py:588
-        self.register_buffer("weight_global_scale", torch.tensor([gs], dtype=torch.float32, device=device))
-        self.register_buffer("act_global_scale", torch.tensor([gs], dtype=torch.float32, device=device))
+        # 3.0 whenever the method is abs_max, for both formats, like the reference's pre_forward (linear.py:206-217:
+        # its abs_max branch comes before the NVFP4 one); exported WUSH checkpoints carry their own value (10.0 for
+        # NVFP4, wush_gptq.py:588) and overwrite it through the state dict.  Buffers in the module dtype, as there.
+        self.register_buffer("weight_global_scale", torch.tensor([3.0], **kw))
+        self.register_buffer("act_global_scale", torch.tensor([3.0], **kw))
         cols = in_features if config.transform_init == "wush" else g
         self.register_buffer("forward_hadamard_matrix", torch.zeros(g, cols, **kw))
+        self.register_buffer("backward_hadamard_matrix", torch.zeros(g, cols, **kw))
+        # blocked weight scales and alpha are derived from the buffers on first use and whenever the buffers are
+        # replaced or written (load_state_dict copies in place, .to() / .cuda() replace the tensors)
+        self._derived_key = None
         self._scales_blocked: Optional[torch.Tensor] = None
         self._alpha: Optional[torch.Tensor] = None
+        self._quantized = False
 
     # -- weights ---------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -101,18 +108,21 @@ class FPQuantLinear(nn.Module):
         """Build the transform (unless it is a WUSH matrix, which is loaded) and quantize ``weight`` once
         (reference: linear.py:165-265)."""
         cfg, g = self.config, self.config.hadamard_group_size
+        if cfg.transform_init == "wush":
+            # the matrix and the quantized weights come from the checkpoint (linear.py:183-186); they may already
+            # have been copied into the buffers by load_state_dict
+            self.weight = None
+            self._quantized = True
+            return
         dev, dt = self.weight.device, self.weight.dtype
         if cfg.transform_init == "hadamard":
-            self.forward_hadamard_matrix = _hadamard(g, dev, dt)
+            mat = _hadamard(g, dev, dt)
         elif cfg.transform_init == "identity":
-            self.forward_hadamard_matrix = torch.eye(g, device=dev, dtype=dt)
-        elif cfg.transform_init != "wush":
+            mat = torch.eye(g, device=dev, dtype=dt)
+        else:
             raise ValueError(f"Invalid transform init: {cfg.transform_init}")
-        if cfg.transform_init == "wush":
-            return                      # weights and matrix arrive through load_quantized()
-        q, s = forward_quantize(self.weight.data, self.forward_hadamard_matrix, self.weight_global_scale,
-                                cfg.forward_dtype, cfg.forward_method)
-        self.load_quantized(q, s[: self.out_features, : self.in_features // g], self.forward_hadamard_matrix)
+        q, s = forward_quantize(self.weight.data, mat, self.weight_global_scale, cfg.forward_dtype, cfg.forward_method)
+        self.load_quantized(q, s[: self.out_features, : self.in_features // g], mat)
 
     @torch.no_grad()
     def load_quantized(self, qweight: torch.Tensor, scales: torch.Tensor, matrix: torch.Tensor,
@@ -120,28 +130,50 @@ class FPQuantLinear(nn.Module):
                        act_global_scale: Optional[torch.Tensor] = None) -> None:
         """Take the tensors of an exported realquant checkpoint (names as in wush_gptq.py:592-599)."""
         dev = self.qweight.device
+        dt = self.forward_hadamard_matrix.dtype
         self.qweight = qweight.view(torch.uint8).to(dev).contiguous()
         self.scales = scales.view(torch.uint8).to(dev).contiguous()
-        self.forward_hadamard_matrix = matrix.to(device=dev, dtype=torch.bfloat16).contiguous()
+        self.forward_hadamard_matrix = matrix.to(device=dev, dtype=dt).contiguous()
+        self.backward_hadamard_matrix = self.forward_hadamard_matrix.clone()
         if weight_global_scale is not None:
-            self.weight_global_scale = weight_global_scale.to(device=dev, dtype=torch.float32).reshape(1)
+            self.weight_global_scale = weight_global_scale.to(device=dev, dtype=dt).reshape(1)
         if act_global_scale is not None:
-            self.act_global_scale = act_global_scale.to(device=dev, dtype=torch.float32).reshape(1)
-        self._scales_blocked = ops.to_blocked(self.scales)          # once, not per call
-        self._alpha = (1.0 / (self.weight_global_scale * self.act_global_scale)).float()
+            self.act_global_scale = act_global_scale.to(device=dev, dtype=dt).reshape(1)
         self.weight = None
+        self._quantized = True
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        """A checkpoint that carries ``qweight`` is a quantized one: its tensors land in the buffers (a bf16
+        ``weight`` is then neither expected nor kept), which is the reference's loading protocol."""
+        if prefix + "qweight" in state_dict:
+            if prefix + "weight" not in state_dict:
+                self.weight = None
+            self._quantized = True
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+
+    def _derived(self):
+        """(blocked weight scales, alpha) for the buffers as they are now."""
+        s, wg, ag = self.scales, self.weight_global_scale, self.act_global_scale
+        key = (s.data_ptr(), s._version, s.device, wg.data_ptr(), wg._version, ag.data_ptr(), ag._version)
+        if key != self._derived_key:
+            self._scales_blocked = ops.to_blocked(s.contiguous())          # once per set of weights, not per call
+            self._alpha = (1.0 / (wg.float() * ag.float())).reshape(1)
+            self._derived_key = key
+        return self._scales_blocked, self._alpha
 
     # -- forward ---------------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self._scales_blocked is None:
-            raise RuntimeError("call pre_forward() or load_quantized() first")
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """y = x W^T (+ bias) (+ residual): quantize the activations with the layer's transform, multiply in FP4
+        (reference: FPQuant4x16NoMasterFn.forward, linear_fns.py:494-539).  Bias and the optional residual
+        are added in the GEMM's epilogue."""
+        if not self._quantized:
+            raise RuntimeError("call pre_forward() or load_quantized(), or load a quantized state dict, first")
         cfg = self.config
+        scales_blocked, alpha = self._derived()
         x_flat = x.contiguous().flatten(end_dim=-2)
         xq, xs = forward_quantize(x_flat, self.forward_hadamard_matrix, self.act_global_scale, cfg.forward_dtype,
                                   cfg.forward_method, blocked=True)
-        y = ops.matmul_fp4_blocked(xq, self.qweight, xs.view(-1), self._scales_blocked.view(-1), self._alpha,
-                                   _fmt(cfg.forward_dtype))
-        y = y.unflatten(0, x.shape[:-1])
-        if self.bias is not None:
-            y = y + self.bias
-        return y
+        res = residual.contiguous().flatten(end_dim=-2) if residual is not None else None
+        y = ops.matmul_fp4_blocked(xq, self.qweight, xs.view(-1), scales_blocked.view(-1), alpha,
+                                   _fmt(cfg.forward_dtype), bias=self.bias, residual=res)
+        return y.unflatten(0, x.shape[:-1])

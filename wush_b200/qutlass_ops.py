@@ -185,11 +185,17 @@ def to_blocked(x: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 
 def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor, ws_blocked: torch.Tensor,
-                       alpha: torch.Tensor, fmt: str, splits: int = 0) -> torch.Tensor:
+                       alpha: torch.Tensor, fmt: str, splits: int = 0, bias: Optional[torch.Tensor] = None,
+                       residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = alpha * deq(x) @ deq(w)^T in bf16 with scales ALREADY in the blocked layout (what
     ``to_blocked`` returns, or what the fused quantize kernel writes with ``sf_layout=SF_BLOCKED``).
-    x: (..., K/2) u8, w: (N, K/2) u8; fmt 'mx' (E8M0 per 32) or 'nv' (E4M3 per 16)."""
-    _require_cuda(x, w, xs_blocked, ws_blocked, alpha)
+    x: (..., K/2) u8, w: (N, K/2) u8; fmt 'mx' (E8M0 per 32) or 'nv' (E4M3 per 16).
+
+    ``bias`` (bf16 [N]) and ``residual`` (bf16 [..., N], may be ``out``) are added inside the GEMM's epilogue
+    with the roundings of the separate steps they replace (``y += bias`` after forward_gemm, linear_fns.py:523-525,
+    and the decoder block's ``hidden = residual + y``).  ``out`` (bf16 [..., N], rows may be strided) receives the
+    result instead of a new tensor."""
+    _require_cuda(x, w, xs_blocked, ws_blocked, alpha, bias, residual, out)
     if x.dtype != torch.uint8 or w.dtype != torch.uint8:
         raise ValueError("packed FP4 operands must be uint8")
     lead = x.shape[:-1]
@@ -204,19 +210,34 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
     need = lambda rows: (rows + 127) // 128 * 128 * ((k // group + 3) // 4 * 4)
     if xs_blocked.numel() < need(m) or ws_blocked.numel() < need(n):
         raise ValueError("blocked scale tensor smaller than ceil(rows/128)*128 x ceil(K/G/4)*4")
-    y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+
+    def rows_2d(t: torch.Tensor, what: str) -> torch.Tensor:
+        t2 = t.reshape(-1, t.shape[-1]) if t.dim() != 2 else t
+        if t2.dtype != torch.bfloat16 or tuple(t2.shape) != (m, n) or (m > 0 and t2.stride(1) != 1):
+            raise ValueError(f"{what} must be bfloat16 of shape (..., {n}) with unit column stride")
+        return t2
+
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device) if out is None else rows_2d(out, "out")
     if m == 0:
         return y.reshape(*lead, n)
+    res2 = rows_2d(residual, "residual") if residual is not None else None
+    if bias is not None and (bias.dtype != torch.bfloat16 or tuple(bias.shape) != (n,)):
+        raise ValueError(f"bias must be bfloat16 of shape ({n},)")
     lib = _lib.load()
     al = alpha.to(device=x.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
     with torch.cuda.device(x.device):
         ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k)) if splits == 0 else splits * m * n * 4
-        work = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
-        fn = lib.wush_gemm_mxf4_bf16_tn if fmt == "mx" else lib.wush_gemm_nvf4_bf16_tn
-        rc = fn(x2.data_ptr(), w.data_ptr(), xs_blocked.data_ptr(), ws_blocked.data_ptr(), al.data_ptr(), y.data_ptr(),
-                m, n, k, work.data_ptr() if work is not None else None, ws_bytes, splits, None, _stream(x))
+        work = _lib.gemm_workspace(x.device, ws_bytes) if ws_bytes else None
+        rc = lib.wush_gemm_fp4_bf16_tn_fused(
+            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), w.data_ptr(), xs_blocked.data_ptr(),
+            ws_blocked.data_ptr(), al.data_ptr(), bias.contiguous().data_ptr() if bias is not None else None,
+            res2.data_ptr() if res2 is not None else None, res2.stride(0) if res2 is not None else 0, y.data_ptr(),
+            y.stride(0), m, n, k, work.data_ptr() if work is not None else None, work.numel() if work is not None else 0,
+            splits, _lib.status_word(x.device).data_ptr(), _stream(x))
     _lib.check(rc, f"wush_gemm_{fmt}f4_bf16_tn")
-    return y.reshape(*lead, n)
+    if _lib.CHECK_EVERY_OP:
+        _lib.check_status(x.device, "FP4 GEMM")
+    return y.reshape(*lead, n) if out is None else out
 
 
 @torch.library.custom_op("wush_b200::matmul_mxf4_bf16_tn_op", mutates_args=())

@@ -92,7 +92,8 @@ class ColumnShardedFP4Linear:
                 rc = lib.wush_gemm_fp4_bf16_tn_sharded(fmt, xq.data_ptr(), self.qweight.data_ptr(), xs_blocked.data_ptr(),
                                                        self.ws.data_ptr(), self.alpha.data_ptr(), self._ptr_array,
                                                        self.world, self.rank, self.n_total, self.col0, m, self.n_shard,
-                                                       self.k, None, torch.cuda.current_stream().cuda_stream)
+                                                       self.k, _lib.status_word(self.dev).data_ptr(),
+                                                       torch.cuda.current_stream().cuda_stream)
             _lib.check(rc, "wush_gemm_fp4_bf16_tn_sharded")
             self._handle.barrier(channel=1)       # every rank's columns have landed everywhere
             return self._flat[: m * self.n_total].view(m, self.n_total)
