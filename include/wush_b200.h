@@ -233,16 +233,16 @@ WUSH_API int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const i
  *              hold finite scale bytes (zero is fine)
  *   alpha      device pointer to one fp32 (1 / (weight_global_scale * act_global_scale) in the reference)
  *   y          bf16 [m, n] row-major, 16-byte aligned; n % 8 == 0, k % 128 == 0
- *   workspace  device scratch for the split-K partial tiles (fp32 [splits, m, n], 16-byte aligned, contents
- *              irrelevant); needed only when few output tiles exist (small m).  wush_gemm_workspace_bytes() gives
- *              the size the heuristic wants; with a smaller (or NULL) workspace the GEMM runs unsplit.
- *   splits     0 = choose automatically; > 0 forces that many K splits (fails if the workspace is too small)
+ *   splits     0 = choose automatically.  When few output tiles exist (small m: the GEMM then streams the weights
+ *              once and is bound by memory) the K range is split over 2, 4 or 8 CTAs that form a thread-block cluster;
+ *              their fp32 partial tiles meet in distributed shared memory and are added in split order, in the same
+ *              launch, without scratch memory.
+ *              > 0 forces that many K splits the other way: fp32 partial tiles [splits, m, n] in `workspace` and a
+ *              second kernel that adds them (fails with WUSH_ERR_WORKSPACE_TOO_SMALL if the workspace is too small).
+ *   workspace  device scratch for forced splits only (16-byte aligned, contents irrelevant,
+ *              wush_gemm_workspace_bytes() bytes); may be NULL when splits <= 1
  *   status     optional device int set to 1 if a bounded wait inside the kernel ran out; may be NULL
- * fp32 accumulation over the whole K range; one rounding to bf16 at the end.  Split K is one launch: every CTA
- * writes its partial block, and the one that arrives last at the block's counter adds the partials in split order
- * (the result does not depend on which one that is) and writes the output.  The counters are the library's own
- * (a ring in device memory, a fresh segment per launch, zero before and after it); the first split-K call on a
- * device looks up the ring's address and should be made outside any stream capture.
+ * fp32 accumulation over the whole K range; one rounding to bf16 at the end.
  */
 WUSH_API int wush_gemm_mxf4_bf16_tn(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                     const float* alpha, void* y, int64_t m, int64_t n, int64_t k, void* workspace,
@@ -293,8 +293,12 @@ WUSH_API int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b, 
                                             const float* alpha, void* y, int64_t m, int64_t n, int64_t k, int splits,
                                             int* status, void* stream);
 
-/* Scratch bytes the automatic split-K choice would use for this problem on the current device (0 = none). */
-WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+/* Thread-block clusters of `splits` (2, 4 or 8) CTAs of the split-K kernel that the current device can run side by
+ * side (0: none, or no sm_100 device); the automatic split choice keeps one cluster per output tile within it. */
+WUSH_API int wush_gemm_cluster_capacity(int format, int splits);
+
+/* Scratch bytes a GEMM with `splits` forced K splits needs (0 for splits <= 1; the automatic choice needs none). */
+WUSH_API size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int splits);
 
 /*
  * Block-scaled FP4 GEMM with column-sharded weights: y[:, col0 : col0 + n] = alpha * A . B_shard^T, stored into the

@@ -104,6 +104,31 @@ def test_gemm_at_benchmark_shapes(m, n, k):
     del _lib
 
 
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("m", [1, 16, 128])
+def test_gemm_at_decoder_layer_shapes_small_m(n, k, m):
+    """The decode shapes: few output tiles, so the K range is split over the CTAs of a cluster.  All outputs against
+    the oracle, also for a forced split through a workspace (the two-kernel path)."""
+    from wush_b200 import qutlass_ops as ops
+    gen = torch.Generator().manual_seed(n + k + m)
+    aq = torch.randint(0, 256, (m, k // 2), generator=gen, dtype=torch.uint8)
+    bq = torch.randint(0, 256, (n, k // 2), generator=gen, dtype=torch.uint8)
+    asf = torch.randint(122, 130, (m, k // 32), generator=gen, dtype=torch.uint8)
+    bsf = torch.randint(118, 126, (n, k // 32), generator=gen, dtype=torch.uint8)
+    alpha = torch.tensor([1.0 / 9.0], device=DEV)
+    xb, wb = ops.to_blocked(asf.to(DEV)).view(-1), ops.to_blocked(bsf.to(DEV)).view(-1)
+    y = ops.matmul_fp4_blocked(aq.to(DEV), bq.to(DEV), xb, wb, alpha, "mx")
+    y2 = ops.matmul_fp4_blocked(aq.to(DEV), bq.to(DEV), xb, wb, alpha, "mx", splits=2)
+    torch.cuda.synchronize()
+    want = wo.fp4_gemm(aq.numpy(), asf.numpy(), bq.numpy(), bsf.numpy(), 1.0 / 9.0, "mxfp4")
+    got = y.double().cpu().numpy()
+    assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
+    assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+    got2 = y2.double().cpu().numpy()
+    assert np.linalg.norm(got2 - want) <= 1e-2 * np.linalg.norm(want)
+    assert np.abs(got2 - got).max() <= 2.0 ** -7 * np.abs(want).max()
+
+
 def _gpu_activations(tokens: int, hidden: int, seed: int) -> torch.Tensor:
     """The benchmark's calibration activations: N(0,1) with 0.5 % outlier channels x 50, generated on the device in
     slices."""

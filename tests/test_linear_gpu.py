@@ -145,7 +145,8 @@ def test_state_dict_loading_matches_load_quantized(fmt):
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("tokens", [8, 300])
 def test_bias_and_residual_in_the_gemm_epilogue_are_bit_identical_to_separate_adds(fmt, tokens):
-    """tokens = 8 runs the split-K kernel (the last-arriving warp finishes the tile), 300 the CTA-pair kernel."""
+    """tokens = 8 runs the split-K kernel (the CTAs of a cluster add their partial tiles through shared memory and
+    finish the output), 300 the CTA-pair kernel."""
     from wush_b200 import qutlass_ops as ops
     from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
     dev = torch.device("cuda:0")

@@ -68,6 +68,7 @@ def load() -> ctypes.CDLL:
         "wush_hessian_mirror_tiles": [vp, i64, i64, i64, vp],
         "wush_hessian_tiles_per_wave": [],
         "wush_hessian_tile_coords": [i64, i64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+        "wush_gemm_cluster_capacity": [i32, i32],
         "wush_status_check": [vp, vp],
         "wush_selftest_bounded_wait": [vp, i32, vp],
         "wush_gemm_fp4_bf16_tn_fused": [i32, vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, vp,
@@ -84,7 +85,7 @@ def load() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     lib.wush_gemm_mxf4_bf16_tn_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, vp, vp]
     lib.wush_gemm_mxf4_bf16_tn_noalloc.restype = ctypes.c_int
-    lib.wush_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.wush_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.wush_gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.wush_hessian_tile_count.argtypes = [i64]
     lib.wush_hessian_tile_count.restype = ctypes.c_int64

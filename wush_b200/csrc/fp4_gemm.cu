@@ -51,11 +51,10 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_COL0 = 256, SF_STAGE_COLS = 48, SFB_OFF = 16;
 
 constexpr int MAX_PEERS = 8;
-// Split K: one arrival counter per (tile, epilogue warp).  The counters live in a ring inside the library: zero when
-// the library is loaded, returned to zero by every launch, a fresh segment per launch so that launches running side
-// by side on different streams do not share any (at most kCounterRing / 8 tiles can be in flight at once).
-constexpr int kMaxCounters = 2048;            // per launch: 256 tiles
-constexpr int kCounterRing = 1 << 16;
+// Split K inside a thread-block cluster: the CTAs of a cluster share one output tile, each taking a slice of K;
+// their fp32 partial tiles meet in shared memory (see splitk_cluster_finish).
+constexpr int MAX_CLUSTER_SPLITS = 8;          // portable cluster size
+constexpr int CL_ROW_FLOATS = BN + 4;          // padded row of the staged partial tile
 
 struct Params {
   const uint8_t* sfa;   // blocked scales of A: ceil(M/128) row blocks x sf_atoms_k atoms of 512 B
@@ -69,7 +68,8 @@ struct Params {
   int64_t ldy;          // row stride of the output buffers in elements (N, or the unsharded N)
   int64_t ycol0;        // first output column of this GPU's shard inside them
   float* partial;       // [splits, M, N] when splits > 1
-  unsigned int* counters;  // splits > 1: this launch's segment of the arrival-counter ring, zero before and after
+  int cluster_splits;   // splits > 1: 1 = the CTAs of a cluster reduce through shared memory, 0 = fp32 partial tiles
+                        // in global memory and a second kernel
   // optional epilogue terms, applied in the reference's order with its roundings (linear_fns.py:514-525):
   // y = bf16(alpha * acc); y = bf16(y + bias[col]); y = bf16(y + residual[row, col])
   const __nv_bfloat16* bias;       // [N] or null
@@ -316,50 +316,71 @@ __device__ __forceinline__ void drain_and_store(const Params& p, uint32_t taddr,
   }
 }
 
-// Split K: the warp that arrives last at a (tile, warp) counter adds the fp32 partial blocks of all splits (in
-// split order, so the result does not depend on who is last) and writes the bf16 output rows of its 32 x 128
-// block: lane l owns columns 4l .. 4l+3 of every row, so loads are 512 and stores 256 contiguous bytes per row.
-__device__ __forceinline__ void splitk_finish(const Params& p, int row0, int col0, float alpha, int lane) {
-  const int col = col0 + 4 * lane;
-  if (col >= p.n) return;                       // n % 8 == 0: groups of 4 never straddle the edge
-  const int64_t mn = (int64_t)p.m * p.n;
-  float2 b01 = make_float2(0.f, 0.f), b23 = make_float2(0.f, 0.f);
+// bf16(alpha * acc) (+ bias) (+ residual) for 4 consecutive columns, with the roundings of the separate steps.
+__device__ __forceinline__ uint2 finish_f4(const Params& p, float4 acc, float alpha, int row, int col) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * alpha, acc.y * alpha);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * alpha, acc.w * alpha);
   if (p.bias != nullptr) {
     const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + col);
-    b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.x));
-    b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.y));
+    const float2 b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.x));
+    const float2 b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bv.y));
+    const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+    lo = __floats2bfloat162_rn(l.x + b01.x, l.y + b01.y);
+    hi = __floats2bfloat162_rn(h.x + b23.x, h.y + b23.y);
   }
-  const int rows = min(32, p.m - row0);
-  for (int r = 0; r < rows; ++r) {
-    const float* src = p.partial + (int64_t)(row0 + r) * p.n + col;
-    float4 acc = __ldcg(reinterpret_cast<const float4*>(src));
-    for (int s = 1; s < p.splits; ++s) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)s * mn));
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * alpha, acc.y * alpha);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * alpha, acc.w * alpha);
-    if (p.bias != nullptr) {
-      const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
-      lo = __floats2bfloat162_rn(l.x + b01.x, l.y + b01.y);
-      hi = __floats2bfloat162_rn(h.x + b23.x, h.y + b23.y);
-    }
-    if (p.residual != nullptr) {
-      const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + (int64_t)(row0 + r) * p.ldr + col);
-      const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.x));
-      const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.y));
-      const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
-      lo = __floats2bfloat162_rn(l.x + r01.x, l.y + r01.y);
-      hi = __floats2bfloat162_rn(h.x + r23.x, h.y + r23.y);
-    }
-    uint2 o;
-    o.x = *reinterpret_cast<const uint32_t*>(&lo);
-    o.y = *reinterpret_cast<const uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p.y + (int64_t)(row0 + r) * p.ldy + p.ycol0 + col) = o;
+  if (p.residual != nullptr) {
+    const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + (int64_t)row * p.ldr + col);
+    const float2 r01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.x));
+    const float2 r23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rv.y));
+    const float2 l = __bfloat1622float2(lo), h = __bfloat1622float2(hi);
+    lo = __floats2bfloat162_rn(l.x + r01.x, l.y + r01.y);
+    hi = __floats2bfloat162_rn(h.x + r23.x, h.y + r23.y);
+  }
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&lo);
+  o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  return o;
+}
+
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+
+// Split K inside a cluster, second half: every CTA of the cluster has staged the valid rows of its fp32 partial
+// tile in its own shared memory (row stride CL_ROW_FLOATS) and the cluster has synchronised.  CTA `rank` of the
+// `splits` CTAs finishes the column slice [rank, rank + 1) * BN / splits of the tile: it adds the partials of all
+// CTAs in rank order through distributed shared memory and writes the bf16 output.  Called by the 256 epilogue threads.
+__device__ __forceinline__ void splitk_cluster_finish(const Params& p, uint32_t stage_smem, int rank, int splits,
+                                                      int row0, int col0, float alpha, int tid) {
+  const int rows = min(BM, p.m - row0);
+  const int slice = BN / splits;                 // columns per CTA: 32 .. 128, a multiple of 4
+  const int f4_per_row = slice / 4;
+  const int items = rows * f4_per_row;
+  for (int it = tid; it < items; it += 256) {
+    const int r = it / f4_per_row, c = rank * slice + (it % f4_per_row) * 4;
+    if (col0 + c >= p.n) continue;               // n % 8 == 0: groups of 4 never straddle the edge
+    const uint32_t off = stage_smem + (uint32_t)(r * CL_ROW_FLOATS + c) * 4u;
+    float4 v[MAX_CLUSTER_SPLITS];
+#pragma unroll
+    for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s)       // all loads in flight before the first add
+      if (s < splits) v[s] = ld_dsmem_f4(map_to_cta(off, (uint32_t)s));
+    float4 acc = v[0];
+#pragma unroll
+    for (int s = 1; s < MAX_CLUSTER_SPLITS; ++s)
+      if (s < splits) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+    *reinterpret_cast<uint2*>(p.y + (int64_t)(row0 + r) * p.ldy + p.ycol0 + col0 + c) =
+        finish_f4(p, acc, alpha, row0 + r, col0 + c);
   }
 }
 
-template <bool NV>
+// CLUSTER: launched as clusters of p.splits CTAs with exactly one work item per CTA (grid = tiles * splits); the
+// CTAs of a cluster reduce their partial tiles through distributed shared memory.
+template <bool NV, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, const Params p) {
   constexpr int GROUP = NV ? 16 : 32;
@@ -557,8 +578,28 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         drain_and_store(p, taddr, alpha, row - lane, col0, lane, [&] {
           if (lane == 0) mbar_arrive(tempty_bar);
         });
+      } else if (CLUSTER) {
+        // split K inside a cluster: the valid rows of the fp32 partial tile go to this CTA's shared memory (the
+        // pipeline stages are free: every MMA has completed, so every load has landed and been read)
+        float* dst = reinterpret_cast<float*>(smem) + (quarter * 32 + lane) * CL_ROW_FLOATS + half * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.m) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<float4*>(dst + c * 32 + 4 * u) =
+                  make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]),
+                              __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar);
       } else {
-        // split K: fp32 partial tile, stored chunk by chunk before the accumulator is released
+        // split K through global memory: fp32 partial tile, stored chunk by chunk; a second kernel adds the splits
         float* dst = p.partial + ((int64_t)sp * p.m + row) * p.n + col0;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -577,20 +618,19 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar);
-        // count this warp's block as delivered; the last of the `splits` warps sums them (no second kernel)
-        __threadfence();
-        __syncwarp();
-        unsigned int prev = 0;
-        unsigned int* ctr = p.counters + ((mb * p.n_blocks + nb) * 8 + (warp - EPI_WARP0));
-        if (lane == 0) prev = atomicAdd(ctr, 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == (unsigned int)p.splits - 1u) {
-          __threadfence();
-          if (row - lane < p.m) splitk_finish(p, row - lane, col0, alpha, lane);
-          if (lane == 0) *ctr = 0u;          // the counters are zero again when the launch ends
-        }
       }
     }
+  }
+
+  if (CLUSTER) {
+    // every thread of every CTA of the cluster gets here, whatever its role and even after a wait that ran out
+    cluster_sync_all();                 // the partial tiles of all CTAs are staged
+    if (warp >= EPI_WARP0 && warp < SF_WARP0) {
+      int mb, nb, sp;
+      work_coords(p, blockIdx.x, mb, nb, sp);
+      splitk_cluster_finish(p, smem_base, sp, p.splits, mb * BM, nb * BN, *p.alpha, threadIdx.x - EPI_WARP0 * 32);
+    }
+    cluster_sync_all();                 // nobody leaves while its shared memory may still be read
   }
 
   tc_fence_before();
@@ -848,45 +888,30 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
 
+// Split K through global memory, second kernel: add the per-split fp32 partial tiles, scale, add the optional
+// epilogue terms, round to bf16.
+__global__ void splitk_reduce_kernel(const Params p) {
+  const float a = *p.alpha;
+  const int64_t mn = (int64_t)p.m * p.n;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < mn; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(p.partial + i);
+    for (int s = 1; s < p.splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(p.partial + (int64_t)s * mn + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int row = (int)(i / p.n), col = (int)(i - (int64_t)row * p.n);     // n % 8 == 0: 4 values share a row
+    *reinterpret_cast<uint2*>(p.y + (int64_t)row * p.ldy + p.ycol0 + col) = finish_f4(p, acc, a, row, col);
+  }
+}
+
 // K splits for a problem: enough CTAs to occupy the machine when there are few output tiles
 // (small M: the GEMM streams the weights once and is HBM-bound), at least 2 k-blocks per split.
-static int choose_splits(int64_t tiles, int k_blocks, int sms) {
-  if (tiles >= sms || tiles * 8 > kMaxCounters) return 1;
+static int choose_splits(int64_t tiles, int k_blocks, int sms, int cap) {
+  if (tiles >= sms) return 1;
   int64_t s = sms / tiles;
   if (s > k_blocks / 2) s = k_blocks / 2;
-  if (s > 16) s = 16;
+  if (s > cap) s = cap;
   return s < 1 ? 1 : (int)s;
-}
-
-static __device__ __align__(256) unsigned int g_arrival_counters[kCounterRing];
-
-// This launch's `count` counters: the device address of the ring (looked up once per device, with that device
-// current: in host code the array's name is only a handle for the runtime) plus the next free segment.
-static int counter_segment(int count, unsigned int** out) {
-  static unsigned int* base[kMaxDevices] = {};
-  static unsigned int next[kMaxDevices] = {};
-  static std::mutex mu;
-  const int dev = device_slot();
-  if (dev < 0) return WUSH_ERR_BAD_SHAPE;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!base[dev]) {
-    void* p = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&p, g_arrival_counters);
-    if (e != cudaSuccess) return (int)e;
-    base[dev] = static_cast<unsigned int*>(p);
-  }
-  if (next[dev] + (unsigned)count > (unsigned)kCounterRing) next[dev] = 0;
-  *out = base[dev] + next[dev];
-  next[dev] += (unsigned)count;
-  return WUSH_OK;
-}
-
-// After a launch that gave up on a wait the counters it touched may be non-zero: clear the ring (stream order).
-int reset_arrival_counters(cudaStream_t stream) {
-  void* p = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(&p, g_arrival_counters);
-  if (e == cudaSuccess) e = cudaMemsetAsync(p, 0, sizeof(unsigned int) * kCounterRing, stream);
-  return (int)e;
 }
 
 struct Shard {               // column-sharded output: where this GPU's columns go, here and on the other GPUs
@@ -937,6 +962,37 @@ static int cached_operand_map(CUtensorMap* out, const void* base, uint64_t rows,
   return 0;
 }
 
+// Clusters of `splits` CTAs of the split-K kernel that can be resident at once on the current device (each CTA
+// fills an SM; a cluster must fit into one GPC).  Also opts the kernel into its shared memory.  Cached per device.
+static int cluster_capacity(bool nv, int splits) {
+  static PerDevice attr[2], cap[2][4];     // cap[..][log2(splits)]: capacity + 1 (0 = not asked yet)
+  auto ck = nv ? fp4_gemm_kernel<true, true> : fp4_gemm_kernel<false, true>;
+  if (opt_in_smem(attr[nv], ck, SMEM_BYTES) != 0) return 0;
+  int lg = 0;
+  while ((1 << lg) < splits) ++lg;
+  if (lg > 3 || (1 << lg) != splits) return 0;
+  const int dev = device_slot();
+  int state = dev >= 0 ? cap[nv][lg].get(dev) : 0;
+  if (!state) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(splits * (sm_count() / splits)));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute a;
+    a.id = cudaLaunchAttributeClusterDimension;
+    a.val.clusterDim.x = (unsigned)splits;
+    a.val.clusterDim.y = 1;
+    a.val.clusterDim.z = 1;
+    cfg.attrs = &a;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, ck, &cfg) != cudaSuccess || n < 0) n = 0;
+    state = n + 1;
+    if (dev >= 0) cap[nv][lg].set(dev, state);
+  }
+  return state - 1;
+}
+
 static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                        const float* alpha, void* y, int64_t m, int64_t n, int64_t k, float* partial,
                        size_t partial_bytes, int force_splits, int* status, cudaStream_t stream,
@@ -978,20 +1034,28 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   p.status = status;
   const int sms = sm_count();
   const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
-  int splits = force_splits > 0 ? force_splits : choose_splits(tiles, p.k_blocks, sms);
-  if (splits > p.k_blocks) splits = p.k_blocks;
-  const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
-  if (need > partial_bytes || (need && !partial) || (splits > 1 && tiles * 8 > kMaxCounters)) {
-    if (force_splits > 0) return tiles * 8 > kMaxCounters ? WUSH_ERR_TOO_LARGE : WUSH_ERR_WORKSPACE_TOO_SMALL;
-    splits = 1;   // no room for partial tiles: run unsplit
+  // K splits.  Automatic: a power of two up to 8, the CTAs of a split forming a cluster that reduces through
+  // shared memory (no scratch).  Forced by the caller: any count, fp32 partial tiles in the caller's workspace
+  // and a second kernel.
+  int splits = 1;
+  bool cluster = false;
+  if (force_splits > 0) {
+    splits = force_splits > p.k_blocks ? p.k_blocks : force_splits;
+    const size_t need = splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+    if (need > partial_bytes || (need && !partial)) return WUSH_ERR_WORKSPACE_TOO_SMALL;
+    if (splits > 1 && ((uintptr_t)partial & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  } else {
+    // the largest cluster size whose clusters (one per tile) are all resident at once: a second wave of
+    // clusters would double the run time of a launch that is a few microseconds long
+    static const int cap_env = env_int("WUSH_B200_GEMM_MAX_SPLITS", MAX_CLUSTER_SPLITS);
+    const int want = choose_splits(tiles, p.k_blocks, sms, cap_env < MAX_CLUSTER_SPLITS ? cap_env : MAX_CLUSTER_SPLITS);
+    while (splits * 2 <= want) splits *= 2;
+    while (splits > 1 && cluster_capacity(nv, splits) < tiles) splits /= 2;
+    cluster = splits > 1;
   }
-  if (splits > 1 && ((uintptr_t)partial & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   p.splits = splits;
+  p.cluster_splits = cluster ? 1 : 0;
   p.partial = partial;
-  if (splits > 1) {
-    rc = counter_segment((int)tiles * 8, &p.counters);
-    if (rc != 0) return rc;
-  }
 
   CUtensorMap amap, bmap;
   rc = cached_operand_map(&amap, a, (uint64_t)m, (uint64_t)k / 2, BM);
@@ -1033,14 +1097,39 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
 
   rc = cached_operand_map(&bmap, b, (uint64_t)n, (uint64_t)k / 2, BN);
   if (rc != 0) return rc;
-  auto kern = nv ? fp4_gemm_kernel<true> : fp4_gemm_kernel<false>;
+  if (cluster) {
+    auto ck = nv ? fp4_gemm_kernel<true, true> : fp4_gemm_kernel<false, true>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * splits));     // one work item per CTA; cluster c = tile c, rank = split
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = (unsigned)splits;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, ck, amap, bmap, p);
+  }
+  auto kern = nv ? fp4_gemm_kernel<true, false> : fp4_gemm_kernel<false, false>;
   static PerDevice attr_one[2];
   rc = opt_in_smem(attr_one[nv], kern, SMEM_BYTES);
   if (rc != 0) return rc;
   int64_t work = tiles * splits;
   int grid = (int)(work < sms ? work : sms);
   kern<<<grid, THREADS, SMEM_BYTES, stream>>>(amap, bmap, p);
-  return (int)cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (splits > 1) {
+    const int64_t mn = m * n;   // n % 8 == 0, so mn % 4 == 0
+    int64_t blocks = (mn / 4 + 255) / 256;
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+    e = cudaGetLastError();
+  }
+  return (int)e;
 }
 
 static int gemm_with_workspace(bool nv, const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
@@ -1143,13 +1232,13 @@ extern "C" int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b
   const int k_blocks = (int)((k + BK - 1) / BK);
   const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   if (splits == 0) {
-    splits = choose_splits(tiles, k_blocks, wush::sm_count());
+    splits = choose_splits(tiles, k_blocks, wush::sm_count(), 16);
     // keep the partial tiles inside the fixed array, but stay a split-K launch
     while (splits > 2 && (size_t)splits * m * n > kStaticScratchFloats) --splits;
     if (splits < 2) splits = 2;
   }
   if (splits < 2 || splits > k_blocks) return WUSH_ERR_BAD_FLAG;   // K too short to split, or a forced value out of range
-  if ((size_t)splits * (size_t)m * (size_t)n > kStaticScratchFloats || tiles * 8 > kMaxCounters) return WUSH_ERR_TOO_LARGE;
+  if ((size_t)splits * (size_t)m * (size_t)n > kStaticScratchFloats) return WUSH_ERR_TOO_LARGE;
   float* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != WUSH_OK) return rc;
@@ -1157,10 +1246,13 @@ extern "C" int wush_gemm_mxf4_bf16_tn_noalloc(const uint8_t* a, const uint8_t* b
                      (cudaStream_t)stream);
 }
 
-extern "C" size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-  using namespace wush::gemm;
-  if (m <= 0 || n <= 0 || k <= 0) return 0;
-  const int64_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int splits = choose_splits(tiles, (int)((k + BK - 1) / BK), wush::sm_count());
-  return splits > 1 ? (size_t)splits * m * n * sizeof(float) : 0;
+extern "C" size_t wush_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int splits) {
+  if (m <= 0 || n <= 0 || k <= 0 || splits <= 1) return 0;
+  return (size_t)splits * m * n * sizeof(float);
+}
+
+extern "C" int wush_gemm_cluster_capacity(int format, int splits) {
+  if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
+  if (wush::require_sm100() != 0) return 0;
+  return wush::gemm::cluster_capacity(format == WUSH_FORMAT_NVFP4, splits);
 }

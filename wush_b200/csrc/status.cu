@@ -10,10 +10,6 @@
 #include "sm100.cuh"
 
 namespace wush {
-namespace gemm {
-int reset_arrival_counters(cudaStream_t stream);   // fp4_gemm.cu
-}
-
 __global__ void bounded_wait_selftest_kernel(int* status, uint32_t max_polls) {
   __shared__ uint64_t bar;
   __shared__ uint32_t abort_flag;
@@ -41,9 +37,6 @@ extern "C" int wush_status_check(int* status_dev, void* stream) {
   if (host == 0) return WUSH_OK;
   e = cudaMemsetAsync(status_dev, 0, sizeof(int), (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
-  // a split-K GEMM that gave up may have left arrival counters behind
-  const int rc = wush::gemm::reset_arrival_counters((cudaStream_t)stream);
-  if (rc != 0) return rc;
   return WUSH_ERR_DEVICE_TIMEOUT;
 }
 

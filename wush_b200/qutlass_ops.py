@@ -226,7 +226,7 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
     lib = _lib.load()
     al = alpha.to(device=x.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
     with torch.cuda.device(x.device):
-        ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k)) if splits == 0 else splits * m * n * 4
+        ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k, splits))
         work = _lib.gemm_workspace(x.device, ws_bytes) if ws_bytes else None
         rc = lib.wush_gemm_fp4_bf16_tn_fused(
             _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), w.data_ptr(), xs_blocked.data_ptr(),
