@@ -110,6 +110,25 @@ WUSH_API int wush_fused_quantize_nv(const void* x, const void* mat, int64_t mat_
                            int64_t cols, int flags, void* stream);
 
 /*
+ * The same kernels for operands that are column slices of wider tensors: the activations may be a slice of a wider
+ * row-major tensor (row stride ldx elements), and the codes and scales are written into the operand buffers of a
+ * GEMM whose K dimension is wider than this call's columns -- how a tensor-parallel layer assembles the quantized
+ * input of its next GEMM from column shards that were produced on different GPUs (every GPU quantizes the columns it
+ * holds; scale groups never straddle a shard).  No counterpart in the reference, which is single-GPU and always
+ * quantizes whole rows (inference_lib/src/fp_quant/module/linear_fns.py:29-62).
+ *
+ *   format     WUSH_FORMAT_MXFP4 / WUSH_FORMAT_NVFP4 (global_scale is ignored for MXFP4 and may be NULL)
+ *   x, ldx     bf16 [rows, cols], row stride ldx >= cols elements, ldx % 8 == 0
+ *   q, ldq     first byte of this call's codes inside the destination, row stride ldq >= cols / 2 bytes, ldq % 16 == 0
+ *   sf, sf_cols, sf_layout   the destination's scale tensor (sf_cols scale bytes per row, all columns of the GEMM)
+ *   sf_group0  index of this call's first scale group inside a row of sf; a multiple of 4
+ */
+WUSH_API int wush_fused_quantize_strided(int format, const void* x, int64_t ldx, const void* mat, int64_t mat_cols,
+                                         const float* global_scale, uint8_t* q, int64_t ldq, uint8_t* sf,
+                                         int64_t sf_cols, int sf_layout, int64_t sf_group0, int64_t rows, int64_t cols,
+                                         int flags, void* stream);
+
+/*
  * Debug/validation variant of the two calls above: same arithmetic, but also stores the
  * transformed values (after the optional bf16 rounding) as fp32 [rows, cols].  `fmt` is 0 for
  * MXFP4 and 1 for NVFP4 (global_scale may be NULL for MXFP4).  Used by the parity tests for the

@@ -219,3 +219,27 @@ def test_pseudo_quant_wrappers_match_oracle_dequantization():
         assert bad <= 1e-4, bad
     y = pq.pseudoquantize_fp(x.to(dev), "mxfp4")
     assert y.shape == x.shape
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+@pytest.mark.parametrize("blocked", [True, False])
+def test_column_shards_assemble_the_whole_operand(fmt, blocked):
+    """Quantizing column shards one by one into a wider operand (codes with a row stride, scales at a group offset)
+    gives the bytes of quantizing whole rows: what every GPU of a tensor-parallel layer does for its own columns."""
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    rows, cols, shards = 333, 1024 + 256, 5
+    g = GROUP[fmt]
+    x = synth.activations(rows, cols, seed=31).to(dev)
+    mat = synth.to_bf16_tensor(synth.wush_matrix(cols, g, seed=5)).to(dev)
+    gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+    layout = 1 if blocked else 0
+    q_ref, sf_ref = ops._quantize(x, mat, fmt, gs, sf_layout=layout)
+    q = torch.zeros_like(q_ref)
+    sf = torch.zeros_like(sf_ref)
+    per = cols // shards                                      # 256 columns: a multiple of 4 groups in both formats
+    for s in range(shards):
+        xs = x[:, s * per:(s + 1) * per]                      # a column slice: row stride = cols
+        ops.fused_quantize_into(xs, mat[:, s * per:(s + 1) * per].contiguous(), fmt, gs, q, sf, col0=s * per, sf_layout=layout)
+    assert torch.equal(q, q_ref)
+    assert torch.equal(sf, sf_ref)

@@ -47,6 +47,9 @@ struct QuantParams {
   float* transformed;               // debug variant only
   int64_t sf_cols;
   int sf_layout;
+  int64_t ldx;                      // row stride of x in elements
+  int64_t ldq;                      // row stride of q in bytes
+  int64_t sf_group0;                // index of this call's first scale group inside the rows of sf (multiple of 4)
   int64_t rows, cols;
   int row_splits;                   // grid.y: CTAs sharing the rows of one slab
   int round_bf16;
@@ -233,8 +236,8 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   // row and a running source pointer instead of multiplying per tile.
   uint32_t issue_stage_off = 0;
   int issue_row = row_begin + g;                                   // first of this lane's 4 rows of the next tile
-  const __nv_bfloat16* issue_ptr = xcol + (int64_t)issue_row * p.cols;
-  const int64_t row8 = 8 * p.cols, row32 = 32 * p.cols;           // element strides of 8 and 32 rows
+  const __nv_bfloat16* issue_ptr = xcol + (int64_t)issue_row * p.ldx;
+  const int64_t row8 = 8 * p.ldx, row32 = 32 * p.ldx;             // element strides of 8 and 32 rows
   auto issue_tile = [&](int t) {
     if (active && t < n_tiles) {
       const uint32_t dst = ring_wr + issue_stage_off;
@@ -245,7 +248,7 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = min(issue_row + 8 * i, last_row);  // clamp: rows past the end are discarded later
-          cp_async_16(dst + i * (8 * 64), xcol + (int64_t)r * p.cols);
+          cp_async_16(dst + i * (8 * 64), xcol + (int64_t)r * p.ldx);
         }
       }
       issue_row += kTileRows;
@@ -328,13 +331,14 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   const float gs = NV ? *p.global_scale : 0.0f;
   const float gs6 = gs / 6.0f;
   float* tp = DEBUG ? p.transformed + (int64_t)(row_begin + g) * p.cols + col0 + 8 * q4 : nullptr;
-  const int64_t q_stride = p.cols >> 1;
+  const int64_t q_stride = p.ldq;
   // store phase: thread t writes 16 bytes of codes of row t/8, segment t%8 (= chunk) of the slab
   const int st_row = threadIdx.x >> 3, st_seg = threadIdx.x & 7;
   const bool st_ok = slab_col0 + st_seg * kChunk < p.cols;
   uint8_t* q_dst = p.q + (int64_t)(row_begin + st_row) * q_stride + (slab_col0 >> 1) + st_seg * 16;
-  const int sf_slab0 = (int)(slab_col0 / TD);           // first scale group of the slab
+  const int sf_slab0 = (int)(slab_col0 / TD);           // first scale group of the slab (inside this call's columns)
   const int sf_total = (int)(p.cols / TD);
+  const int64_t sf_g0 = p.sf_group0;                    // where this call's groups start inside a row of sf
 
   // loop-invariant ldmatrix offsets inside a stage: [mt][ks]
   uint32_t a_off[2][2];
@@ -424,10 +428,10 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
           const uint32_t word = sv[c];
           uint8_t* dst;
           if (BL) {
-            dst = p.sf + ((int64_t)(row >> 7) * (p.sf_cols >> 2) + (grp >> 2)) * 512 + (row & 31) * 16 +
+            dst = p.sf + ((int64_t)(row >> 7) * (p.sf_cols >> 2) + ((sf_g0 + grp) >> 2)) * 512 + (row & 31) * 16 +
                   ((row >> 5) & 3) * 4;
           } else {
-            dst = p.sf + (int64_t)row * p.sf_cols + grp;
+            dst = p.sf + (int64_t)row * p.sf_cols + sf_g0 + grp;
           }
           if (grp + 4 <= sf_total) {
             *reinterpret_cast<uint32_t*>(dst) = word;
@@ -502,7 +506,7 @@ extern "C" int wush_fused_quantize_mx(const void* x, const void* mat, int64_t ma
   if (rc != WUSH_OK) return rc;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
-                sf_cols, sf_layout, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
   return launch_quant<false, false>(p, (cudaStream_t)stream);
 }
 
@@ -513,7 +517,7 @@ extern "C" int wush_fused_quantize_nv(const void* x, const void* mat, int64_t ma
   if (rc != WUSH_OK) return rc;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, nullptr,
-                sf_cols, sf_layout, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
   return launch_quant<true, false>(p, (cudaStream_t)stream);
 }
 
@@ -528,7 +532,29 @@ extern "C" int wush_fused_quantize_debug(int fmt, const void* x, const void* mat
   if ((uintptr_t)transformed & 15) return WUSH_ERR_BAD_ALIGNMENT;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, transformed,
-                sf_cols, sf_layout, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
   return fmt == 1 ? launch_quant<true, true>(p, (cudaStream_t)stream)
                   : launch_quant<false, true>(p, (cudaStream_t)stream);
+}
+
+extern "C" int wush_fused_quantize_strided(int format, const void* x, int64_t ldx, const void* mat, int64_t mat_cols,
+                                           const float* global_scale, uint8_t* q, int64_t ldq, uint8_t* sf,
+                                           int64_t sf_cols, int sf_layout, int64_t sf_group0, int64_t rows, int64_t cols,
+                                           int flags, void* stream) {
+  if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
+  const bool nv = format == WUSH_FORMAT_NVFP4;
+  const int g = nv ? 16 : 32;
+  if (!x || !mat || !q || !sf || (nv && !global_scale)) return WUSH_ERR_NULL_POINTER;
+  if (rows < 0 || cols <= 0 || cols % 32 != 0) return WUSH_ERR_BAD_SHAPE;
+  if (mat_cols != cols && mat_cols != g) return WUSH_ERR_BAD_SHAPE;
+  if (ldx < cols || ldx % 8 != 0 || ldq < cols / 2 || ldq % 16 != 0) return WUSH_ERR_BAD_SHAPE;
+  if (sf_group0 < 0 || sf_group0 % 4 != 0 || sf_cols % 4 != 0 || sf_cols < sf_group0 + cols / g) return WUSH_ERR_BAD_SHAPE;
+  if (sf_layout != WUSH_SF_ROW_MAJOR && sf_layout != WUSH_SF_BLOCKED) return WUSH_ERR_BAD_FLAG;
+  if (flags & ~WUSH_QUANT_ROUND_BF16) return WUSH_ERR_BAD_FLAG;
+  if (((uintptr_t)x & 15) || ((uintptr_t)q & 15) || ((uintptr_t)sf & 3)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (mat_cols == cols && ((uintptr_t)mat & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (rows == 0) return WUSH_OK;
+  QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, nullptr,
+                sf_cols, sf_layout, ldx, ldq, sf_group0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+  return nv ? launch_quant<true, false>(p, (cudaStream_t)stream) : launch_quant<false, false>(p, (cudaStream_t)stream);
 }

@@ -78,6 +78,43 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
     return q, sf
 
 
+def fused_quantize_into(x: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor],
+                        q_out: torch.Tensor, sf_out: torch.Tensor, col0: int = 0, sf_layout: int = _lib.SF_BLOCKED,
+                        round_bf16: bool = False) -> None:
+    """Transform + quantize the columns ``x`` holds and write them into a wider GEMM operand: codes into
+    ``q_out[:, col0/2 : (col0 + cols)/2]`` and scales into the matching groups of ``sf_out`` (the scale tensor of the
+    WHOLE operand: ``ceil(K/G/4)*4`` bytes per row, row-major 2-D or blocked).  ``x`` may be a column slice of a wider
+    tensor.  This is how a layer whose input columns are spread over GPUs assembles its quantized operand: scale
+    groups never straddle a shard, so every GPU quantizes what it holds."""
+    _require_cuda(x, matrix, global_scale, q_out, sf_out)
+    group = 32 if fmt == "mx" else 16
+    rows, cols = x.shape
+    if x.dtype != torch.bfloat16 or matrix.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise ValueError("x and the transform matrix must be bfloat16, x with unit column stride")
+    if q_out.dtype != torch.uint8 or q_out.dim() != 2 or q_out.shape[0] < rows or q_out.stride(1) != 1:
+        raise ValueError("q_out must be a uint8 [rows, K/2] tensor")
+    k_total = q_out.shape[1] * 2
+    if col0 % (4 * group) or col0 + cols > k_total:
+        raise ValueError(f"col0 must be a multiple of {4 * group} and the slice must fit into the operand")
+    sf_cols = (k_total // group + 3) // 4 * 4
+    pr = (rows + 127) // 128 * 128
+    if sf_out.numel() < (pr if sf_layout == _lib.SF_BLOCKED else rows) * sf_cols:
+        raise ValueError("sf_out is smaller than the operand's scale tensor")
+    matrix = matrix.contiguous()
+    if rows == 0:
+        return
+    gs = None
+    if fmt == "nv":
+        gs = global_scale.to(device=x.device, dtype=torch.float32).reshape(-1)[:1].contiguous()
+    with torch.cuda.device(x.device):
+        rc = _lib.load().wush_fused_quantize_strided(
+            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x.data_ptr(), x.stride(0), matrix.data_ptr(),
+            matrix.shape[1], gs.data_ptr() if gs is not None else None, q_out.data_ptr() + col0 // 2, q_out.stride(0),
+            sf_out.data_ptr(), sf_cols, sf_layout, col0 // group, rows, cols, _lib.QUANT_ROUND_BF16 if round_bf16 else 0,
+            _stream(x))
+    _lib.check(rc, "wush_fused_quantize_strided")
+
+
 # --------------------------------------------------------------------------------------------
 # forward quantization (reference: qutlass_ops.py:37-143)
 # --------------------------------------------------------------------------------------------
