@@ -97,3 +97,33 @@ def test_gemm_cta_pair_kernel_in_subprocess():
     env = dict(os.environ, WUSH_B200_GEMM_PAIR="1")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0 and "pair ok" in out.stdout, out.stdout + out.stderr
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+@pytest.mark.parametrize("m", [16, 200, 700])
+def test_activations_given_as_stacked_k_shards(fmt, m):
+    """The K dimension of the activations in pieces that were quantized separately and stacked (how column shards
+    from different GPUs arrive): same bits as the GEMM on the whole rows.  m = 16 runs the cluster split-K kernel,
+    200 and 700 the CTA-pair kernel."""
+    from wush_b200 import qutlass_ops as ops
+    dev = torch.device("cuda:0")
+    shards, ks, n = 4, 512, 384
+    k = shards * ks
+    g = 32 if fmt == "mx" else 16
+    x = synth.activations(m, k, seed=3).to(dev)
+    w = synth.weights(n, k, seed=4).to(dev)
+    had = synth.to_bf16_tensor(synth.hadamard_matrix(g)).to(dev)
+    gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+    alpha = torch.tensor([1.0 / 9.0 if fmt == "mx" else 0.01], device=dev)
+    xq, xs = ops._quantize(x, had, fmt, gs, sf_layout=1)
+    wq, ws = ops._quantize(w, had, fmt, gs, sf_layout=1)
+    want = ops.matmul_fp4_blocked(xq, wq, xs.view(-1), ws.view(-1), alpha, fmt)
+    rows_alloc = 768                                          # more rows than used, as in a buffer sized for the largest batch
+    stack_q = torch.zeros(shards, rows_alloc, ks // 2, dtype=torch.uint8, device=dev)
+    stack_s = torch.zeros(shards, rows_alloc * (ks // g), dtype=torch.uint8, device=dev)
+    for s in range(shards):
+        q, sf = ops._quantize(x[:, s * ks:(s + 1) * ks].contiguous(), had, fmt, gs, sf_layout=1)
+        stack_q[s, :m] = q
+        stack_s[s, : sf.numel()] = sf.view(-1)
+    got = ops.matmul_fp4_blocked(stack_q, wq, stack_s.view(-1), ws.view(-1), alpha, fmt, rows=m)
+    assert torch.equal(got, want)

@@ -79,6 +79,12 @@ struct Params {
   int m_blocks, n_blocks, k_blocks;   // k_blocks of BK elements (the last may be half)
   int splits;           // CTAs sharing the K range of one tile
   int sf_atoms_k;       // 512-byte atoms per 128-row block = ceil(K/group/4)
+  // A given as K shards stacked one after the other (each [a_shard_rows, K/shards/2] codes with its own blocked
+  // scale tensor): the layout in which column shards quantized on different GPUs arrive.  a_kbs = 0: plain A.
+  int a_kbs;            // k-blocks per shard
+  int a_shard_rows;     // rows of the tensor map between two shards
+  int a_sf_atoms;       // 512-byte scale atoms per 128-row block inside one shard
+  int64_t a_sf_shard_bytes;   // bytes between the scale tensors of two shards
   int sfb_row_blocks;   // 128-row blocks present in sfb
   int* status;
 };
@@ -188,6 +194,23 @@ __device__ __forceinline__ bool umma_fp4_x4_probe(uint32_t d_tmem, uint64_t ad, 
 __device__ __forceinline__ uint32_t make_idesc_fp4(bool nv, uint32_t sf_id, uint32_t m = BM) {
   return (sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((nv ? 0u : 1u) << 23) |
          ((m >> 4) << 24) | (sf_id << 29);
+}
+
+// Where k-block kb of the A rows starting at `row` lives: tensor-map coordinates and scale-atom address.
+__device__ __forceinline__ void a_coords(const Params& p, int kb, int row, int& x, int& y) {
+  if (p.a_kbs == 0) {
+    x = kb * (BK / 2);
+    y = row;
+  } else {
+    const int sh = kb / p.a_kbs;
+    x = (kb - sh * p.a_kbs) * (BK / 2);
+    y = sh * p.a_shard_rows + row;
+  }
+}
+__device__ __forceinline__ const uint8_t* a_scale_atoms(const Params& p, int kb, int row_block, int atoms_per_kb) {
+  if (p.a_kbs == 0) return p.sfa + ((int64_t)row_block * p.sf_atoms_k + kb * atoms_per_kb) * 512;
+  const int sh = kb / p.a_kbs;
+  return p.sfa + sh * p.a_sf_shard_bytes + ((int64_t)row_block * p.a_sf_atoms + (kb - sh * p.a_kbs) * atoms_per_kb) * 512;
 }
 
 // work item -> (m block, n block, split); m fastest so neighbouring CTAs share a weight panel
@@ -440,7 +463,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (!(ok = mbar_wait(empty_bar(s), (round & 1) ^ 1, abort_flag))) break;
           mbar_arrive_expect_tx(full_bar(s), A_BYTES + B_BYTES);
           const uint32_t dst = smem_base + s * STAGE_BYTES;
-          tma_load_2d(dst, &amap, kb * (BK / 2), mb * BM, full_bar(s));
+          int ax, ay;
+          a_coords(p, kb, mb * BM, ax, ay);
+          tma_load_2d(dst, &amap, ax, ay, full_bar(s));
           tma_load_2d(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN, full_bar(s));
           if (++s == STAGES) { s = 0; ++round; }
         }
@@ -467,7 +492,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const uint32_t sf_bytes = (uint32_t)atoms * 512u;
           mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * (1 + b_blocks));
           const uint32_t dst = smem_base + s * STAGE_BYTES + A_BYTES + B_BYTES;
-          bulk_load(dst, p.sfa + ((int64_t)mb * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
+          bulk_load(dst, a_scale_atoms(p, kb, mb, ATOMS), sf_bytes, sffull_bar(s));
           for (int r = 0; r < b_blocks; ++r)
             bulk_load(dst + SFA_BYTES + r * (SFB_BYTES / 2),
                       p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
@@ -737,7 +762,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
           if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (A_BYTES + P_B_BYTES));
           const uint32_t full_leader = map_to_cta(full_bar(s), 0);
           const uint32_t dst = smem_base + s * P_STAGE_BYTES;
-          tma_load_2d_pair(dst, &amap, kb * (BK / 2), a_blk * 128, full_leader);
+          int ax, ay;
+          a_coords(p, kb, a_blk * 128, ax, ay);
+          tma_load_2d_pair(dst, &amap, ax, ay, full_leader);
           tma_load_2d_pair(dst + A_BYTES, &bmap, kb * (BK / 2), nb * BN + (int)rank * 128, full_leader);
           if (++s == P_STAGES) { s = 0; ++round; }
         }
@@ -761,7 +788,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_cons
           mbar_arrive_expect_tx(sffull_bar(s), sf_bytes * ((a_sf ? 1 : 0) + b_blocks));
           const uint32_t dst = smem_base + s * P_STAGE_BYTES + A_BYTES + P_B_BYTES;
           if (a_sf)
-            bulk_load(dst, p.sfa + ((int64_t)a_blk * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
+            bulk_load(dst, a_scale_atoms(p, kb, a_blk, ATOMS), sf_bytes, sffull_bar(s));
           for (int r = 0; r < b_blocks; ++r)
             bulk_load(dst + G::SFA_B + r * (G::SFB_B / 2),
                       p.sfb + ((int64_t)(nb * 2 + r) * p.sf_atoms_k + kb * ATOMS) * 512, sf_bytes, sffull_bar(s));
@@ -920,11 +947,13 @@ struct Shard {               // column-sharded output: where this GPU's columns 
   int64_t ldy = 0, col0 = 0;
 };
 
-struct Epilogue {            // optional terms added to the output, and its row stride
+struct Epilogue {            // optional terms added to the output, its row stride, and a K-sharded A operand
   const void* bias = nullptr;
   const void* residual = nullptr;
   int64_t ldr = 0;
   int64_t ldy = 0;           // 0: n
+  int a_shards = 1;          // > 1: A is `a_shards` stacked [a_shard_rows, k / a_shards / 2] matrices
+  int64_t a_shard_rows = 0;
 };
 
 // Tensor maps are pure functions of (base pointer, shape, box), and encoding one costs about a microsecond
@@ -1058,7 +1087,17 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
   p.partial = partial;
 
   CUtensorMap amap, bmap;
-  rc = cached_operand_map(&amap, a, (uint64_t)m, (uint64_t)k / 2, BM);
+  if (epi && epi->a_shards > 1) {
+    const int64_t ks = k / epi->a_shards;
+    if (k % epi->a_shards || ks % BK || epi->a_shard_rows < m) return WUSH_ERR_BAD_SHAPE;
+    p.a_kbs = (int)(ks / BK);
+    p.a_shard_rows = (int)epi->a_shard_rows;
+    p.a_sf_atoms = (int)(ks / group / 4);
+    p.a_sf_shard_bytes = (int64_t)((epi->a_shard_rows + 127) / 128) * p.a_sf_atoms * 512;
+    rc = cached_operand_map(&amap, a, (uint64_t)epi->a_shard_rows * epi->a_shards, (uint64_t)ks / 2, BM);
+  } else {
+    rc = cached_operand_map(&amap, a, (uint64_t)m, (uint64_t)k / 2, BM);
+  }
   if (rc != 0) return rc;
 
   // large M, unsplit: 256 x 256 tiles on CTA pairs
@@ -1156,14 +1195,16 @@ extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const 
                                          status, stream, nullptr);
 }
 
-extern "C" int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, const uint8_t* b, const uint8_t* sfa,
-                                           const uint8_t* sfb, const float* alpha, const void* bias,
-                                           const void* residual, int64_t ldr, void* y, int64_t ldy, int64_t m,
-                                           int64_t n, int64_t k, void* workspace, size_t workspace_bytes, int splits,
-                                           int* status, void* stream) {
+extern "C" int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, int a_shards, int64_t a_shard_rows,
+                                           const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                                           const void* bias, const void* residual, int64_t ldr, void* y, int64_t ldy,
+                                           int64_t m, int64_t n, int64_t k, void* workspace, size_t workspace_bytes,
+                                           int splits, int* status, void* stream) {
   if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
+  if (a_shards < 1 || a_shards > 64) return WUSH_ERR_BAD_SHAPE;
   wush::gemm::Epilogue epi;
   epi.bias = bias; epi.residual = residual; epi.ldr = ldr; epi.ldy = ldy;
+  epi.a_shards = a_shards; epi.a_shard_rows = a_shard_rows;
   return wush::gemm::gemm_with_workspace(format == WUSH_FORMAT_NVFP4, a, b, sfa, sfb, alpha, y, m, n, k, workspace,
                                          workspace_bytes, splits, status, stream, &epi);
 }

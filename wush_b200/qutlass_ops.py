@@ -223,7 +223,8 @@ def to_blocked(x: torch.Tensor) -> torch.Tensor:
 
 def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor, ws_blocked: torch.Tensor,
                        alpha: torch.Tensor, fmt: str, splits: int = 0, bias: Optional[torch.Tensor] = None,
-                       residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                       rows: Optional[int] = None) -> torch.Tensor:
     """y = alpha * deq(x) @ deq(w)^T in bf16 with scales ALREADY in the blocked layout (what
     ``to_blocked`` returns, or what the fused quantize kernel writes with ``sf_layout=SF_BLOCKED``).
     x: (..., K/2) u8, w: (N, K/2) u8; fmt 'mx' (E8M0 per 32) or 'nv' (E4M3 per 16).
@@ -231,21 +232,35 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
     ``bias`` (bf16 [N]) and ``residual`` (bf16 [..., N], may be ``out``) are added inside the GEMM's epilogue
     with the roundings of the separate steps they replace (``y += bias`` after forward_gemm, linear_fns.py:523-525,
     and the decoder block's ``hidden = residual + y``).  ``out`` (bf16 [..., N], rows may be strided) receives the
-    result instead of a new tensor."""
+    result instead of a new tensor.
+
+    ``rows`` given: ``x`` is a STACK of K shards, uint8 [shards, rows_alloc, K/shards/2] (rows_alloc >= rows), and
+    ``xs_blocked`` the stack of their blocked scale tensors -- activations whose columns were quantized in pieces
+    (on different GPUs) and copied side by side; the first ``rows`` rows of every piece are multiplied."""
     _require_cuda(x, w, xs_blocked, ws_blocked, alpha, bias, residual, out)
     if x.dtype != torch.uint8 or w.dtype != torch.uint8:
         raise ValueError("packed FP4 operands must be uint8")
-    lead = x.shape[:-1]
-    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    group = 32 if fmt == "mx" else 16
     w = w.contiguous()
-    m, kb = x2.shape
     n = w.shape[0]
+    a_shards, a_shard_rows = 1, 0
+    if rows is not None:
+        if x.dim() != 3 or not x.is_contiguous() or rows > x.shape[1]:
+            raise ValueError("a stacked operand must be a contiguous [shards, rows_alloc, K/shards/2] tensor")
+        a_shards, a_shard_rows, kb = x.shape[0], x.shape[1], x.shape[0] * x.shape[2]
+        lead, x2, m = (rows,), x, rows
+        if (x.shape[2] * 2) % 256:
+            raise ValueError("every K shard must be a multiple of 256 columns")
+        need_a = a_shards * ((a_shard_rows + 127) // 128 * 128) * (x.shape[2] * 2 // group)
+    else:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        m, kb = x2.shape
+        need_a = (m + 127) // 128 * 128 * ((kb * 2 // group + 3) // 4 * 4)
     if w.shape[1] != kb:
         raise ValueError(f"K mismatch: x has {kb * 2}, w has {w.shape[1] * 2}")
     k = kb * 2
-    group = 32 if fmt == "mx" else 16
-    need = lambda rows: (rows + 127) // 128 * 128 * ((k // group + 3) // 4 * 4)
-    if xs_blocked.numel() < need(m) or ws_blocked.numel() < need(n):
+    if xs_blocked.numel() < need_a or ws_blocked.numel() < (n + 127) // 128 * 128 * ((k // group + 3) // 4 * 4):
         raise ValueError("blocked scale tensor smaller than ceil(rows/128)*128 x ceil(K/G/4)*4")
 
     def rows_2d(t: torch.Tensor, what: str) -> torch.Tensor:
@@ -266,7 +281,8 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
         ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k, splits))
         work = _lib.gemm_workspace(x.device, ws_bytes) if ws_bytes else None
         rc = lib.wush_gemm_fp4_bf16_tn_fused(
-            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), w.data_ptr(), xs_blocked.data_ptr(),
+            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), a_shards, a_shard_rows, w.data_ptr(),
+            xs_blocked.data_ptr(),
             ws_blocked.data_ptr(), al.data_ptr(), bias.contiguous().data_ptr() if bias is not None else None,
             res2.data_ptr() if res2 is not None else None, res2.stride(0) if res2 is not None else 0, y.data_ptr(),
             y.stride(0), m, n, k, work.data_ptr() if work is not None else None, work.numel() if work is not None else 0,
