@@ -627,10 +627,115 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
             "clocks": clocks.summary()}
 
 
+BLOCK_TOKENS, BLOCK_SEQ = 16 * 2048, 2048
+
+
+def bench_block(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind) -> dict:
+    """The seven W4A4 linears (plus attention, norms, SwiGLU) of one decoder block of a hidden-8192 / 64-head /
+    8-KV-head / FFN-28672 model on 16 x 2048 tokens, weights column-sharded over the GPUs, FP4 codes exchanged
+    through NVLink by the copy engines while the other micro-batch multiplies.  Parity: the first sequence of the
+    timed configuration against a step-by-step restatement (dequantized codes, fp32 matmuls) of the whole block
+    computed on every rank with the unsharded weights."""
+    import torch.nn.functional as F
+    from oracle import synth
+    from wush_b200.block import BlockConfig, ShardedDecoderBlock, quantize_block_weights
+    from wush_b200.gptq import dequantize
+    from wush_b200 import qutlass_ops as ops
+    cfg = BlockConfig()
+    H, FF, d = cfg.hidden, cfg.ffn, cfg.head_dim
+    kv = cfg.n_kv_heads * d
+    gen = torch.Generator(device=dev).manual_seed(31)           # the same weights on every rank
+    shapes = {"q": (H, H), "k": (kv, H), "v": (kv, H), "o": (H, H), "gate": (FF, H), "up": (FF, H), "down": (H, FF)}
+    had = synth.to_bf16_tensor(synth.hadamard_matrix(32))
+    transforms = {"attn_in": synth.to_bf16_tensor(synth.wush_matrix(H, 32, seed=41)), "o": had,
+                  "mlp_in": synth.to_bf16_tensor(synth.wush_matrix(H, 32, seed=42)),
+                  "down": synth.to_bf16_tensor(synth.wush_matrix(FF, 32, seed=43))}
+    qw = {}
+    for name, (r, c) in shapes.items():
+        w = (torch.randn(r, c, generator=gen, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        qw.update(quantize_block_weights(cfg, {name: w}, transforms, dev))
+        del w
+    gammas = (torch.ones(H, dtype=torch.bfloat16), torch.ones(H, dtype=torch.bfloat16))
+    hs = H // world
+    h_full0 = torch.randn(BLOCK_SEQ, H, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)   # sequence 0
+    h = torch.randn(BLOCK_TOKENS, hs, generator=torch.Generator(device=dev).manual_seed(50 + rank), device=dev,
+                    dtype=torch.float32).to(torch.bfloat16)
+    h[:BLOCK_SEQ] = h_full0[:, rank * hs:(rank + 1) * hs]
+    blk = ShardedDecoderBlock(cfg, qw, transforms, gammas, BLOCK_SEQ, BLOCK_TOKENS, dev, micro_batches=2 if world > 1 else 1)
+
+    # ---- parity on sequence 0 (before the timed loop changes h) ---------------------------------------------
+    first = blk.forward(h.clone())[:BLOCK_SEQ].float()
+
+    def linear(x, t, names):
+        q, sf = ops._quantize(x.contiguous(), t.to(dev), "mx", None)
+        xd = dequantize(q, sf[: x.shape[0], : x.shape[1] // 32], "mxfp4")
+        outs = []
+        for nme in names:
+            wd = dequantize(*qw[nme], "mxfp4")
+            outs.append((xd @ wd.t()).to(torch.bfloat16))
+            del wd
+        return outs
+
+    def norm(x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)).to(torch.bfloat16)
+
+    old_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    hr = h_full0.clone()
+    q_, k_, v_ = linear(norm(hr), transforms["attn_in"], ("q", "k", "v"))
+    sh = lambda t, nh: t.view(1, BLOCK_SEQ, nh, d).transpose(1, 2)
+    o = F.scaled_dot_product_attention(sh(q_, cfg.n_heads), sh(k_, cfg.n_kv_heads), sh(v_, cfg.n_kv_heads), is_causal=True,
+                                       enable_gqa=True)
+    hr = linear(o.transpose(1, 2).reshape(BLOCK_SEQ, -1), had, ("o",))[0] + hr
+    g_, u_ = linear(norm(hr), transforms["mlp_in"], ("gate", "up"))
+    want = (linear(F.silu(g_) * u_, transforms["down"], ("down",))[0] + hr)[:, rank * hs:(rank + 1) * hs].float()
+    torch.backends.cuda.matmul.allow_tf32 = old_tf32
+    err = torch.stack([(first - want).norm() ** 2, want.norm() ** 2])
+    if world > 1:
+        dist.all_reduce(err)
+    rel = float((err[0] / err[1]).sqrt())
+    del want, first, hr, g_, u_, q_, k_, v_, o
+
+    steps = max(2, min(args.steps, 8))
+    for _ in range(2):
+        blk.forward(h)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        e0.record()
+        for _ in range(steps):
+            blk.forward(h)
+        e1.record()
+        barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    lin_flops = 2.0 * BLOCK_TOKENS * (H * (H + 2 * kv) + H * H + 3 * H * FF)
+    code_bytes = BLOCK_TOKENS * (3 * H + FF) * (0.5 + 1.0 / 32) * (world - 1) / world       # received per rank
+    return {"metric": "w4a4_decoder_block_forward_ms", "value": ms, "unit": "ms per block", "ms_per_step": ms,
+            "higher_is_better": False, "scaling": "strong", "steps": steps,
+            "linear_TFLOPS": lin_flops / (ms * 1e-3) / 1e12,
+            "frac_of_nominal_dense_fp4_per_gpu": lin_flops / (ms * 1e-3) / 1e12 / world / FP4_NOMINAL_TFLOPS,
+            "model_forward_ms_80_blocks": 80 * ms,
+            "nvlink_bytes_received_per_rank": code_bytes, "nvlink_floor_ms": code_bytes / 770e9 * 1e3,
+            "config": {"workload": f"one decoder block, hidden {H}, {cfg.n_heads} heads / {cfg.n_kv_heads} KV heads, FFN {FF}, "
+                                   f"{BLOCK_TOKENS // BLOCK_SEQ} x {BLOCK_SEQ} tokens, MXFP4 W4A4 (per-group WUSH matrices on "
+                                   f"the q/k/v, gate/up and down inputs, Hadamard on the o_proj input), weight rows of all "
+                                   f"seven linears sharded over {world} GPU(s); attention = torch SDPA on local heads; "
+                                   f"embedding and lm_head (not quantized in the reference) are not part of it"},
+            "gpu_launches": steps * 8 * (2 if world > 1 else 1),
+            "parity": _parity("block_70b", rel, 1e-2, "relative Frobenius error of the block output on the first sequence vs a "
+                              "step-by-step fp32 restatement with the unsharded weights (all ranks)"),
+            "clocks": clocks.summary()}
+
+
 def _compact(sec: dict) -> dict:
     """The figures of a section a reader of the one-line record needs."""
     out = {k: sec[k] for k in ("metric", "value", "unit", "ms_per_step", "combine_path", "fused_ms", "nccl_ms",
-                               "rtn_ms_per_layer", "gptq_ms_per_layer", "frac") if k in sec}
+                               "rtn_ms_per_layer", "gptq_ms_per_layer", "frac", "linear_TFLOPS",
+                               "frac_of_nominal_dense_fp4_per_gpu", "model_forward_ms_80_blocks") if k in sec}
     if "roofline" in sec:
         out["frac"] = sec["roofline"]["frac"]
         out["peak_kind"] = sec["roofline"]["peak_kind"]
@@ -681,6 +786,7 @@ def run_ours(args) -> None:
               "decode": lambda: bench_decode(args, dev, torch, ops, peaks, peak_kind),
               "sharded": lambda: bench_sharded_gemm(args, dev, torch, dist, world, barrier),
               "sweep": lambda: bench_sweep(args, dev, torch),
+              "block": lambda: bench_block(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind),
               "hessian": lambda: bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind,
                                                HESS_HIDDEN=args.hess_hidden)}
     if args.only in single:
@@ -783,6 +889,7 @@ def run_ours(args) -> None:
             extra["sweep"] = single["sweep"]()
         else:
             extra["sharded"] = single["sharded"]()
+        extra["block_70b"] = single["block"]()
 
     if rank == 0:
         value = world * alg * args.steps / (ms * 1e-3) / 1e9
@@ -882,7 +989,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
-    ap.add_argument("--only", default="all", choices=["all", "quant", "quant_nv", "gemm", "gemm_nv", "decode", "hessian", "sweep", "sharded"],
+    ap.add_argument("--only", default="all", choices=["all", "quant", "quant_nv", "gemm", "gemm_nv", "decode", "hessian", "sweep", "sharded", "block"],
                     help="run one section only (profiler captures of a single kernel on a small case)")
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)

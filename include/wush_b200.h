@@ -282,13 +282,15 @@ WUSH_API int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const ui
  *   a_shards   1: `a` is [m, k/2] as above.  > 1: the K dimension of the activations arrives in `a_shards` pieces
  *              that were quantized separately (e.g. column shards produced on different GPUs and copied side by
  *              side): `a` is a stack of a_shards matrices [a_shard_rows, k/a_shards/2] (a_shard_rows >= m), and
- *              `sfa` a stack of their blocked scale tensors (ceil(a_shard_rows/128)*128 rows x k/a_shards/G groups
- *              each); k/a_shards must be a multiple of 256.  The weights are unaffected: piece s multiplies the
- *              weight columns [s, s+1) * k/a_shards.
+ *              `sfa` a stack of their blocked scale tensors, a_sf_shard_bytes apart (0 = densely stacked:
+ *              ceil(a_shard_rows/128)*128 rows x k/a_shards/G groups each; otherwise a multiple of 16);
+ *              k/a_shards must be a multiple of 256.  The weights are unaffected: piece s multiplies the weight
+ *              columns [s, s+1) * k/a_shards.
  * Everything else as for wush_gemm_mxf4_bf16_tn.
  */
 WUSH_API int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, int a_shards, int64_t a_shard_rows,
-                                         const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                                         int64_t a_sf_shard_bytes, const uint8_t* b, const uint8_t* sfa,
+                                         const uint8_t* sfb, const float* alpha,
                                          const void* bias, const void* residual, int64_t ldr, void* y, int64_t ldy,
                                          int64_t m, int64_t n, int64_t k, void* workspace, size_t workspace_bytes,
                                          int splits, int* status, void* stream);

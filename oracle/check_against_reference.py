@@ -53,4 +53,7 @@ def run(ref_root: str, seeds=(11, 12, 13)) -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(run(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("WUSH_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: check_against_reference.py <reference checkout>   (or set WUSH_REFERENCE_ROOT)")
+    sys.exit(run(root))

@@ -196,7 +196,9 @@ def sweep_vectors(root: str) -> None:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("WUSH_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py <reference checkout> [sweep]   (or set WUSH_REFERENCE_ROOT)")
     if len(sys.argv) > 2 and sys.argv[2] == "sweep":
         sweep_vectors(root)
     else:

@@ -173,3 +173,51 @@ def test_bias_and_residual_in_the_gemm_epilogue_are_bit_identical_to_separate_ad
     ops.matmul_fp4_blocked(xq, layer.qweight, xs.view(-1), scales_blocked.view(-1), alpha,
                            "mx" if fmt == "mxfp4" else "nv", bias=layer.bias, residual=buf, out=buf)
     assert torch.equal(buf, want)
+
+
+def test_single_layer_pipeline_at_4096_through_a_checkpoint_file(tmp_path):
+    """One 4096 x 4096 layer end to end at the size of the reference's CPU-runnable case: second moment from 16 x 2048
+    calibration tokens, MXFP4 round-to-nearest sweep with WUSH transforms, checkpoint written to disk and read
+    back, real-quant forward of 2048 tokens.  The layer loaded from the file must give the bits of the layer filled in
+    memory, and both must agree with the CPU pseudo-quantizer (oracle sweep on sampled weight rows with the transforms
+    the GPU chose, oracle activation quantizer, float64 product) within 1e-2."""
+    from wush_b200 import checkpoint, gptq
+    from wush_b200.hessian import DistributedHessian
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    hidden, tokens = 4096, 2048
+    dh = DistributedHessian(hidden, dev)
+    for i in range(16):
+        dh.update(synth.activations(2048, hidden, seed=500 + i).to(dev)[None])
+    h = dh.finalize()
+    assert dh.num_samples == 16 * 2048
+    w = synth.weights(hidden, hidden, seed=520)
+    res = gptq.gptq_babai_sweep(w.to(dev), h, "mxfp4", "wush", force_rtn=True)
+    entry = gptq.export_realquant({"transform_basis": res["transform_basis"], "qweight": res["qweight"],
+                                   "scale_quant": res["scale_quant"], "global_scale": res["global_scale"]}, "mxfp4")
+    name = "model.layers.0.self_attn.q_proj"
+    checkpoint.export_quantized_model(str(tmp_path), {name: entry}, None, {"hidden_size": hidden}, hadamard_group_size=32,
+                                      format="mxfp", transform_class="wush")
+    from_file = checkpoint.load_quantized_layers(str(tmp_path), device=dev)[name]
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, hadamard_group_size=32, transform_init="wush")
+    in_memory = FPQuantLinear(hidden, hidden, cfg, bias=False, device=dev)
+    in_memory.load_quantized(entry["qweight"], entry["scales"], entry["forward_hadamard_matrix"],
+                             entry["weight_global_scale"], entry["act_global_scale"])
+    x = synth.activations(tokens, hidden, seed=530)
+    y_file, y_mem = from_file(x.to(dev)), in_memory(x.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(y_file, y_mem)
+    # CPU pseudo-quantizer on sampled output features
+    rows = np.sort(np.random.default_rng(0).choice(hidden, size=64, replace=False))
+    t = res["transform_basis"].double().cpu().numpy()
+    h64 = h.double().cpu().numpy()
+    ref_w = wo.gptq_babai_outer(synth.bf16_to_f64(w)[rows], h64, "mxfp4", "wush", True, transform_fn=lambda b, basis, y: t[b])
+    got_scales = res["scale_quant"].view(torch.uint8).cpu().numpy()[rows]
+    got_codes = wo.unpack_e2m1_codes(res["qweight"].cpu().numpy()[rows])
+    assert np.array_equal(got_scales, ref_w["scale_quant"])
+    assert np.mean(got_codes != ref_w["codes"]) <= 1e-3
+    mat = wo.transform_to_matrix(t)
+    ref_x = wo.fused_transform_quant(synth.bf16_to_f64(x), mat, "mxfp4")["fake_quant"]
+    want = ref_x @ ref_w["fake_quant"].T
+    got = y_mem.double().cpu().numpy()[:, rows]
+    assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)

@@ -5,11 +5,12 @@ import sys
 
 import pytest
 
-REF = os.environ.get("WUSH_REFERENCE_ROOT", "/root/reference")
+from tests.util_reference import REF, needs_reference
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src", "quantization")), reason="no reference checkout")
+@needs_reference
 def test_oracle_matches_reference_code():
     env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
     p = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "check_against_reference.py"), REF],

@@ -72,7 +72,7 @@ def load() -> ctypes.CDLL:
         "wush_gemm_cluster_capacity": [i32, i32],
         "wush_status_check": [vp, vp],
         "wush_selftest_bounded_wait": [vp, i32, vp],
-        "wush_gemm_fp4_bf16_tn_fused": [i32, vp, i32, i64, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, vp,
+        "wush_gemm_fp4_bf16_tn_fused": [i32, vp, i32, i64, i64, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, vp,
                                         ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_mxf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],
         "wush_gemm_nvf4_bf16_tn": [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, i32, vp, vp],

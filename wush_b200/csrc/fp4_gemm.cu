@@ -954,6 +954,7 @@ struct Epilogue {            // optional terms added to the output, its row stri
   int64_t ldy = 0;           // 0: n
   int a_shards = 1;          // > 1: A is `a_shards` stacked [a_shard_rows, k / a_shards / 2] matrices
   int64_t a_shard_rows = 0;
+  int64_t a_sf_shard_bytes = 0;   // bytes between the scale tensors of two shards (0: densely stacked)
 };
 
 // Tensor maps are pure functions of (base pointer, shape, box), and encoding one costs about a microsecond
@@ -1093,7 +1094,9 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
     p.a_kbs = (int)(ks / BK);
     p.a_shard_rows = (int)epi->a_shard_rows;
     p.a_sf_atoms = (int)(ks / group / 4);
-    p.a_sf_shard_bytes = (int64_t)((epi->a_shard_rows + 127) / 128) * p.a_sf_atoms * 512;
+    p.a_sf_shard_bytes = epi->a_sf_shard_bytes ? epi->a_sf_shard_bytes
+                                               : (int64_t)((epi->a_shard_rows + 127) / 128) * p.a_sf_atoms * 512;
+    if (p.a_sf_shard_bytes % 16) return WUSH_ERR_BAD_ALIGNMENT;
     rc = cached_operand_map(&amap, a, (uint64_t)epi->a_shard_rows * epi->a_shards, (uint64_t)ks / 2, BM);
   } else {
     rc = cached_operand_map(&amap, a, (uint64_t)m, (uint64_t)k / 2, BM);
@@ -1196,7 +1199,8 @@ extern "C" int wush_gemm_nvf4_bf16_tn(const uint8_t* a, const uint8_t* b, const 
 }
 
 extern "C" int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, int a_shards, int64_t a_shard_rows,
-                                           const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                                           int64_t a_sf_shard_bytes, const uint8_t* b, const uint8_t* sfa,
+                                           const uint8_t* sfb, const float* alpha,
                                            const void* bias, const void* residual, int64_t ldr, void* y, int64_t ldy,
                                            int64_t m, int64_t n, int64_t k, void* workspace, size_t workspace_bytes,
                                            int splits, int* status, void* stream) {
@@ -1204,7 +1208,7 @@ extern "C" int wush_gemm_fp4_bf16_tn_fused(int format, const uint8_t* a, int a_s
   if (a_shards < 1 || a_shards > 64) return WUSH_ERR_BAD_SHAPE;
   wush::gemm::Epilogue epi;
   epi.bias = bias; epi.residual = residual; epi.ldr = ldr; epi.ldy = ldy;
-  epi.a_shards = a_shards; epi.a_shard_rows = a_shard_rows;
+  epi.a_shards = a_shards; epi.a_shard_rows = a_shard_rows; epi.a_sf_shard_bytes = a_sf_shard_bytes;
   return wush::gemm::gemm_with_workspace(format == WUSH_FORMAT_NVFP4, a, b, sfa, sfb, alpha, y, m, n, k, workspace,
                                          workspace_bytes, splits, status, stream, &epi);
 }

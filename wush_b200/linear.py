@@ -108,7 +108,7 @@ class FPQuantLinear(nn.Module):
         """Build the transform (unless it is a WUSH matrix, which is loaded) and quantize ``weight`` once
         (reference: linear.py:165-265)."""
         cfg, g = self.config, self.config.hadamard_group_size
-        if cfg.transform_init == "wush":
+        if cfg.transform_init == "wush" or self.weight is None:
             # the matrix and the quantized weights come from the checkpoint (linear.py:183-186); they may already
             # have been copied into the buffers by load_state_dict
             self.weight = None

@@ -224,7 +224,7 @@ def to_blocked(x: torch.Tensor) -> torch.Tensor:
 def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor, ws_blocked: torch.Tensor,
                        alpha: torch.Tensor, fmt: str, splits: int = 0, bias: Optional[torch.Tensor] = None,
                        residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                       rows: Optional[int] = None) -> torch.Tensor:
+                       rows: Optional[int] = None, scale_shard_bytes: int = 0) -> torch.Tensor:
     """y = alpha * deq(x) @ deq(w)^T in bf16 with scales ALREADY in the blocked layout (what
     ``to_blocked`` returns, or what the fused quantize kernel writes with ``sf_layout=SF_BLOCKED``).
     x: (..., K/2) u8, w: (N, K/2) u8; fmt 'mx' (E8M0 per 32) or 'nv' (E4M3 per 16).
@@ -236,7 +236,8 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
 
     ``rows`` given: ``x`` is a STACK of K shards, uint8 [shards, rows_alloc, K/shards/2] (rows_alloc >= rows), and
     ``xs_blocked`` the stack of their blocked scale tensors -- activations whose columns were quantized in pieces
-    (on different GPUs) and copied side by side; the first ``rows`` rows of every piece are multiplied."""
+    (on different GPUs) and copied side by side; the first ``rows`` rows of every piece are multiplied.
+    ``scale_shard_bytes`` is the distance between the scale tensors of two pieces when they are not densely stacked."""
     _require_cuda(x, w, xs_blocked, ws_blocked, alpha, bias, residual, out)
     if x.dtype != torch.uint8 or w.dtype != torch.uint8:
         raise ValueError("packed FP4 operands must be uint8")
@@ -251,7 +252,8 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
         lead, x2, m = (rows,), x, rows
         if (x.shape[2] * 2) % 256:
             raise ValueError("every K shard must be a multiple of 256 columns")
-        need_a = a_shards * ((a_shard_rows + 127) // 128 * 128) * (x.shape[2] * 2 // group)
+        need_a = (a_shards - 1) * scale_shard_bytes + (rows + 127) // 128 * 128 * (x.shape[2] * 2 // group) \
+            if scale_shard_bytes else a_shards * ((a_shard_rows + 127) // 128 * 128) * (x.shape[2] * 2 // group)
     else:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
@@ -281,7 +283,8 @@ def matmul_fp4_blocked(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tenso
         ws_bytes = int(lib.wush_gemm_workspace_bytes(m, n, k, splits))
         work = _lib.gemm_workspace(x.device, ws_bytes) if ws_bytes else None
         rc = lib.wush_gemm_fp4_bf16_tn_fused(
-            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), a_shards, a_shard_rows, w.data_ptr(),
+            _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x2.data_ptr(), a_shards, a_shard_rows, scale_shard_bytes,
+            w.data_ptr(),
             xs_blocked.data_ptr(),
             ws_blocked.data_ptr(), al.data_ptr(), bias.contiguous().data_ptr() if bias is not None else None,
             res2.data_ptr() if res2 is not None else None, res2.stride(0) if res2 is not None else 0, y.data_ptr(),
