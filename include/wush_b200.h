@@ -122,11 +122,27 @@ WUSH_API int wush_fused_quantize_nv(const void* x, const void* mat, int64_t mat_
  *   q, ldq     first byte of this call's codes inside the destination, row stride ldq >= cols / 2 bytes, ldq % 16 == 0
  *   sf, sf_cols, sf_layout   the destination's scale tensor (sf_cols scale bytes per row, all columns of the GEMM)
  *   sf_group0  index of this call's first scale group inside a row of sf; a multiple of 4
+ *   row_scale, col_scale   both NULL, or fp32 [rows] and bf16 [cols]: the activations are replaced by
+ *              bf16(bf16(x * row_scale[row]) * col_scale[col]) before the transform -- RMSNorm folded into the
+ *              quantizer of the layer that follows it (row_scale = rsqrt(mean(x^2) + eps) of the WHOLE row, which
+ *              with column shards is formed from wush_row_sumsq partial sums of all GPUs; col_scale = the norm's
+ *              weight), with the roundings of the separate bf16 steps.  Not with WUSH_QUANT_ROUND_BF16.
  */
 WUSH_API int wush_fused_quantize_strided(int format, const void* x, int64_t ldx, const void* mat, int64_t mat_cols,
                                          const float* global_scale, uint8_t* q, int64_t ldq, uint8_t* sf,
-                                         int64_t sf_cols, int sf_layout, int64_t sf_group0, int64_t rows, int64_t cols,
-                                         int flags, void* stream);
+                                         int64_t sf_cols, int sf_layout, int64_t sf_group0, const float* row_scale,
+                                         const void* col_scale, int64_t rows, int64_t cols, int flags, void* stream);
+
+/*
+ * Element-wise neighbours of the quantized layers in a decoder block, one pass over HBM each.  No counterpart in
+ * the reference, whose layers (inference_lib/src/fp_quant/module/linear.py) leave them to the model code.
+ *   wush_row_sumsq  out[r] = sum_c x[r, c]^2 in fp32 (bf16 x [rows, cols], row stride ldx; cols % 8 == 0)
+ *   wush_swiglu     out = bf16(silu(gate)) * up, all bf16 [rows, cols]; gate and up share the row stride ld_in (e.g.
+ *                   the two halves of a fused gate/up projection's output); silu uses the hardware exponential
+ */
+WUSH_API int wush_row_sumsq(const void* x, int64_t ldx, float* out, int64_t rows, int64_t cols, void* stream);
+WUSH_API int wush_swiglu(const void* gate, const void* up, int64_t ld_in, void* out, int64_t ld_out, int64_t rows,
+                         int64_t cols, void* stream);
 
 /*
  * Debug/validation variant of the two calls above: same arithmetic, but also stores the

@@ -243,3 +243,37 @@ def test_column_shards_assemble_the_whole_operand(fmt, blocked):
         ops.fused_quantize_into(xs, mat[:, s * per:(s + 1) * per].contiguous(), fmt, gs, q, sf, col0=s * per, sf_layout=layout)
     assert torch.equal(q, q_ref)
     assert torch.equal(sf, sf_ref)
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+@pytest.mark.parametrize("rows,cols", [(77, 512), (1024, 4096)])
+def test_rmsnorm_folded_into_the_quantizer_is_bit_identical_to_the_separate_steps(fmt, rows, cols):
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    g = GROUP[fmt]
+    x = (synth.activations(rows, cols, seed=41).float() * 0.3).to(torch.bfloat16).to(dev)
+    gamma = (1.0 + 0.2 * torch.randn(cols, generator=torch.Generator().manual_seed(2))).to(torch.bfloat16).to(dev)
+    mat = synth.to_bf16_tensor(synth.wush_matrix(cols, g, seed=6)).to(dev)
+    gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+    ssq = ops.row_sumsq(x)
+    want_ssq = x.double().pow(2).sum(-1)
+    assert float(((ssq.double() - want_ssq).abs() / want_ssq).max()) <= 1e-6
+    rstd = torch.rsqrt(ssq / cols + 1e-5)
+    normed = (x.float() * rstd[:, None]).to(torch.bfloat16) * gamma            # the separate steps, in torch
+    q_ref, sf_ref = ops._quantize(normed, mat, fmt, gs, sf_layout=1)
+    q, sf = torch.zeros_like(q_ref), torch.zeros_like(sf_ref)
+    ops.fused_quantize_into(x, mat, fmt, gs, q, sf, row_scale=rstd, col_scale=gamma)
+    assert torch.equal(q, q_ref) and torch.equal(sf, sf_ref)
+
+
+def test_swiglu_pass_matches_torch():
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    gu = (synth.activations(300, 2 * 1536, seed=9).float() * 0.5).to(torch.bfloat16).to(dev)
+    gate, up = gu[:, :1536], gu[:, 1536:]                       # column halves of one tensor
+    got = ops.swiglu(gate, up)
+    want = torch.nn.functional.silu(gate) * up
+    diff = (got.float() - want.float()).abs()
+    ulp = want.float().abs() * 2.0 ** -7                        # one bf16 step at the value's magnitude, at most
+    assert bool((diff <= ulp + 1e-30).all())
+    assert float((diff > 0).float().mean()) <= 5e-3             # hardware exponential: a rare last-bit difference

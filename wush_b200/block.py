@@ -18,7 +18,8 @@ every rank runs the fused transform + quantize kernel on the columns it holds an
 (0.53 bytes per element instead of 2 for bf16) into the same slot of every rank's operand buffer: one contiguous
 device-to-device copy per peer, which the copy engines carry over NVLink while the SMs multiply.  The GEMM reads its
 activations as a stack of K shards (`rows=` of qutlass_ops.matmul_fp4_blocked).  RMSNorm needs the sum of squares of
-whole rows: the per-rank partial sums (4 bytes per token) travel the same way.
+whole rows: the per-rank partial sums (4 bytes per token) travel the same way, and the normalisation itself is folded
+into the quantize kernel (its row_scale / col_scale prologue), as SwiGLU is a single pass.
 
 Overlap.  The tokens are cut into micro-batches that run on separate streams: while one micro-batch multiplies, the
 codes of the other are in flight.  Buffers live in torch symmetric memory; a stage's exchange ends with one
@@ -95,9 +96,10 @@ class _Exchange:
         self.codes = self.flat.view(world, self.rows_per_slot, pitch)      # the GEMM's stacked operand
         self.scales = self.flat[code_bytes:]                               # first scale tensor; the others `slot` bytes on
 
-    def put(self, x: torch.Tensor, matrix: torch.Tensor, fmt: str, gs) -> None:
+    def put(self, x: torch.Tensor, matrix: torch.Tensor, fmt: str, gs, row_scale=None, col_scale=None) -> None:
         m = x.shape[0]
-        ops.fused_quantize_into(x, matrix, fmt, gs, self.my_codes[:m], self.my_scales, col0=0, sf_layout=_lib.SF_BLOCKED)
+        ops.fused_quantize_into(x, matrix, fmt, gs, self.my_codes[:m], self.my_scales, col0=0, sf_layout=_lib.SF_BLOCKED,
+                                row_scale=row_scale, col_scale=col_scale)
         if self.world > 1:
             lo, hi = self.rank * self.slot, (self.rank + 1) * self.slot
             for i in range(1, self.world):
@@ -189,11 +191,11 @@ class ShardedDecoderBlock:
                       for _ in range(micro_batches)]
 
     # -- pieces ---------------------------------------------------------------------------------------------
-    def _norm(self, h: torch.Tensor, sums: _RowSums, gamma: torch.Tensor) -> torch.Tensor:
-        hf = h.float()
-        total = sums.total(hf.pow(2).sum(-1))
-        rstd = torch.rsqrt(total / self.cfg.hidden + self.cfg.rms_eps)
-        return (hf * rstd[:, None]).to(torch.bfloat16) * gamma
+    def _rstd(self, h: torch.Tensor, sums: _RowSums) -> torch.Tensor:
+        """1 / rms of every WHOLE row of the residual stream: local sums of squares, added over the ranks.  The
+        scaling itself (and the norm's weight) is applied inside the quantize kernel that follows."""
+        total = sums.total(ops.row_sumsq(h))
+        return torch.rsqrt(total / self.cfg.hidden + self.cfg.rms_eps)
 
     def _attention(self, qkv: torch.Tensor) -> torch.Tensor:
         d, s = self.cfg.head_dim, self.seq_len
@@ -209,15 +211,14 @@ class ShardedDecoderBlock:
         cfg, fmt, m = self.cfg, self.cfg.fmt, h.shape[0]
         a, b = slot["h"]
         # attention half
-        a.put(self._norm(h, slot["ssq"][0], self.gamma[0]), self.t["attn_in"], fmt, self.gs)
+        a.put(h, self.t["attn_in"], fmt, self.gs, row_scale=self._rstd(h, slot["ssq"][0]), col_scale=self.gamma[0])
         qkv = a.gemm(m, *self.w["qkv"], self.alpha, fmt)
         b.put(self._attention(qkv), self.t["o"], fmt, self.gs)
         b.gemm(m, *self.w["o"], self.alpha, fmt, residual=h, out=h)            # h += o_proj(...) in the epilogue
         # MLP half
-        a.put(self._norm(h, slot["ssq"][1], self.gamma[1]), self.t["mlp_in"], fmt, self.gs)
+        a.put(h, self.t["mlp_in"], fmt, self.gs, row_scale=self._rstd(h, slot["ssq"][1]), col_scale=self.gamma[1])
         gu = a.gemm(m, *self.w["gate_up"], self.alpha, fmt)
-        act = F.silu(gu[:, : self.fs]) * gu[:, self.fs:]
-        slot["f"].put(act, self.t["down"], fmt, self.gs)
+        slot["f"].put(ops.swiglu(gu[:, : self.fs], gu[:, self.fs:]), self.t["down"], fmt, self.gs)
         slot["f"].gemm(m, *self.w["down"], self.alpha, fmt, residual=h, out=h)
         del cfg
 

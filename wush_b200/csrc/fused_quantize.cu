@@ -53,6 +53,11 @@ struct QuantParams {
   int64_t rows, cols;
   int row_splits;                   // grid.y: CTAs sharing the rows of one slab
   int round_bf16;
+  // optional prologue: x is replaced by bf16(bf16(x * row_scale[row]) * col_scale[col]) before the transform --
+  // RMSNorm applied on the fly (row_scale = 1 / rms of the row, col_scale = the norm's weight), with the roundings
+  // of the separate bf16 steps
+  const float* row_scale;           // fp32 [rows] or null
+  const __nv_bfloat16* col_scale;   // bf16 [cols] or null (both or none)
 };
 
 __device__ __forceinline__ void mma_bf16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -197,8 +202,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 }
 
 // RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
-// the transformed values.
-template <bool NV, bool DEBUG, bool RB, bool BL>
+// the transformed values.  PRO: scale the activations by row_scale / col_scale first (see QuantParams).
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false>
 __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
   constexpr int TD = NV ? 16 : 32;       // transform size == quantization group
   constexpr int GPC = kChunk / TD;       // scale groups per chunk
@@ -330,6 +335,15 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
 
   const float gs = NV ? *p.global_scale : 0.0f;
   const float gs6 = gs / 6.0f;
+  // prologue: this lane's column factors, bf16 pairs for channels 16ks + 8h + 2q + {0,1} of the chunk
+  uint32_t gam[2][2] = {{0, 0}, {0, 0}};
+  if (PRO && active) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        gam[ks][h] = *reinterpret_cast<const uint32_t*>(p.col_scale + col0 + 16 * ks + 8 * h + 2 * q4);
+  }
   float* tp = DEBUG ? p.transformed + (int64_t)(row_begin + g) * p.cols + col0 + 8 * q4 : nullptr;
   const int64_t q_stride = p.ldq;
   // store phase: thread t writes 16 bytes of codes of row t/8, segment t%8 (= chunk) of the slab
@@ -377,6 +391,23 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
         uint32_t a0[4], a1[4];
         ldmatrix_x4(a0, tile + a_off[mt][0]);
         ldmatrix_x4(a1, tile + a_off[mt][1]);
+        if (PRO) {
+          // registers 0/2 hold row g + 16mt, registers 1/3 row g + 8 + 16mt; 0/1 channels 2q.., 2/3 channels 8 + 2q..
+          const float rs0 = p.row_scale[min(r0 + g + 16 * mt, last_row)];
+          const float rs1 = p.row_scale[min(r0 + g + 8 + 16 * mt, last_row)];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float rs = (i & 1) ? rs1 : rs0;
+            float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a0[i]));
+            __nv_bfloat162 r = __floats2bfloat162_rn(f.x * rs, f.y * rs);
+            r = __hmul2(r, *reinterpret_cast<const __nv_bfloat162*>(&gam[0][i >> 1]));
+            a0[i] = *reinterpret_cast<const uint32_t*>(&r);
+            f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a1[i]));
+            r = __floats2bfloat162_rn(f.x * rs, f.y * rs);
+            r = __hmul2(r, *reinterpret_cast<const __nv_bfloat162*>(&gam[1][i >> 1]));
+            a1[i] = *reinterpret_cast<const uint32_t*>(&r);
+          }
+        }
         float acc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -447,7 +478,7 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
 // Grid: x = slabs, y = row splits.  Every CTA takes an equal share (+-1) of the 32-row tiles.
 // The number of row splits is the largest that keeps all CTAs co-resident in `waves` waves of
 // (SMs x CTAs per SM), so the last wave is not a mostly empty tail.
-template <bool NV, bool DEBUG, bool RB, bool BL>
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
   const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
@@ -463,7 +494,7 @@ static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   if (splits > 65535) splits = 65535;
   p.row_splits = (int)splits;
   dim3 grid((unsigned)slabs, (unsigned)splits);
-  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL>;
+  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO>;
   constexpr int smem = kQuantSmem;
   static PerDevice attr_set;     // per instantiation and device
   const int rc = opt_in_smem(attr_set, kern, smem);
@@ -476,6 +507,11 @@ template <bool NV, bool DEBUG>
 static int launch_quant(const QuantParams& p, cudaStream_t stream) {
   if (const int rc100 = require_sm100()) return rc100;
   const bool rb = p.round_bf16 != 0, bl = p.sf_layout == WUSH_SF_BLOCKED;
+  if (p.row_scale != nullptr) {
+    // the prologue exists for the production path only (no bf16 rounding of the transformed values, no debug output)
+    if (DEBUG || rb) return WUSH_ERR_BAD_FLAG;
+    return bl ? launch_quant_t<NV, false, false, true, true>(p, stream) : launch_quant_t<NV, false, false, false, true>(p, stream);
+  }
   if (rb) return bl ? launch_quant_t<NV, DEBUG, true, true>(p, stream) : launch_quant_t<NV, DEBUG, true, false>(p, stream);
   return bl ? launch_quant_t<NV, DEBUG, false, true>(p, stream) : launch_quant_t<NV, DEBUG, false, false>(p, stream);
 }
@@ -506,7 +542,7 @@ extern "C" int wush_fused_quantize_mx(const void* x, const void* mat, int64_t ma
   if (rc != WUSH_OK) return rc;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
-                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
   return launch_quant<false, false>(p, (cudaStream_t)stream);
 }
 
@@ -517,7 +553,7 @@ extern "C" int wush_fused_quantize_nv(const void* x, const void* mat, int64_t ma
   if (rc != WUSH_OK) return rc;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, nullptr,
-                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
   return launch_quant<true, false>(p, (cudaStream_t)stream);
 }
 
@@ -532,15 +568,15 @@ extern "C" int wush_fused_quantize_debug(int fmt, const void* x, const void* mat
   if ((uintptr_t)transformed & 15) return WUSH_ERR_BAD_ALIGNMENT;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, transformed,
-                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
   return fmt == 1 ? launch_quant<true, true>(p, (cudaStream_t)stream)
                   : launch_quant<false, true>(p, (cudaStream_t)stream);
 }
 
 extern "C" int wush_fused_quantize_strided(int format, const void* x, int64_t ldx, const void* mat, int64_t mat_cols,
                                            const float* global_scale, uint8_t* q, int64_t ldq, uint8_t* sf,
-                                           int64_t sf_cols, int sf_layout, int64_t sf_group0, int64_t rows, int64_t cols,
-                                           int flags, void* stream) {
+                                           int64_t sf_cols, int sf_layout, int64_t sf_group0, const float* row_scale,
+                                           const void* col_scale, int64_t rows, int64_t cols, int flags, void* stream) {
   if (format != WUSH_FORMAT_MXFP4 && format != WUSH_FORMAT_NVFP4) return WUSH_ERR_BAD_FLAG;
   const bool nv = format == WUSH_FORMAT_NVFP4;
   const int g = nv ? 16 : 32;
@@ -553,8 +589,11 @@ extern "C" int wush_fused_quantize_strided(int format, const void* x, int64_t ld
   if (flags & ~WUSH_QUANT_ROUND_BF16) return WUSH_ERR_BAD_FLAG;
   if (((uintptr_t)x & 15) || ((uintptr_t)q & 15) || ((uintptr_t)sf & 3)) return WUSH_ERR_BAD_ALIGNMENT;
   if (mat_cols == cols && ((uintptr_t)mat & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  if ((row_scale == nullptr) != (col_scale == nullptr)) return WUSH_ERR_NULL_POINTER;
+  if (((uintptr_t)row_scale & 3) || ((uintptr_t)col_scale & 3)) return WUSH_ERR_BAD_ALIGNMENT;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, nullptr,
-                sf_cols, sf_layout, ldx, ldq, sf_group0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0};
+                sf_cols, sf_layout, ldx, ldq, sf_group0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0,
+                row_scale, (const __nv_bfloat16*)col_scale};
   return nv ? launch_quant<true, false>(p, (cudaStream_t)stream) : launch_quant<false, false>(p, (cudaStream_t)stream);
 }

@@ -80,13 +80,24 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
 
 def fused_quantize_into(x: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor],
                         q_out: torch.Tensor, sf_out: torch.Tensor, col0: int = 0, sf_layout: int = _lib.SF_BLOCKED,
-                        round_bf16: bool = False) -> None:
+                        round_bf16: bool = False, row_scale: Optional[torch.Tensor] = None,
+                        col_scale: Optional[torch.Tensor] = None) -> None:
     """Transform + quantize the columns ``x`` holds and write them into a wider GEMM operand: codes into
     ``q_out[:, col0/2 : (col0 + cols)/2]`` and scales into the matching groups of ``sf_out`` (the scale tensor of the
     WHOLE operand: ``ceil(K/G/4)*4`` bytes per row, row-major 2-D or blocked).  ``x`` may be a column slice of a wider
     tensor.  This is how a layer whose input columns are spread over GPUs assembles its quantized operand: scale
-    groups never straddle a shard, so every GPU quantizes what it holds."""
-    _require_cuda(x, matrix, global_scale, q_out, sf_out)
+    groups never straddle a shard, so every GPU quantizes what it holds.
+
+    ``row_scale`` (fp32 [rows]) and ``col_scale`` (bf16 [cols]) fold an RMSNorm into the call: the kernel quantizes
+    ``bf16(bf16(x * row_scale[:, None]) * col_scale)`` without that tensor ever being written."""
+    _require_cuda(x, matrix, global_scale, q_out, sf_out, row_scale, col_scale)
+    if (row_scale is None) != (col_scale is None):
+        raise ValueError("row_scale and col_scale go together")
+    if row_scale is not None:
+        if row_scale.dtype != torch.float32 or row_scale.numel() != x.shape[0] or not row_scale.is_contiguous():
+            raise ValueError("row_scale must be a contiguous float32 [rows] tensor")
+        if col_scale.dtype != torch.bfloat16 or col_scale.numel() != x.shape[1] or not col_scale.is_contiguous():
+            raise ValueError("col_scale must be a contiguous bfloat16 [cols] tensor")
     group = 32 if fmt == "mx" else 16
     rows, cols = x.shape
     if x.dtype != torch.bfloat16 or matrix.dtype != torch.bfloat16 or x.stride(1) != 1:
@@ -110,9 +121,37 @@ def fused_quantize_into(x: torch.Tensor, matrix: torch.Tensor, fmt: str, global_
         rc = _lib.load().wush_fused_quantize_strided(
             _lib.FORMAT_MXFP4 if fmt == "mx" else _lib.FORMAT_NVFP4, x.data_ptr(), x.stride(0), matrix.data_ptr(),
             matrix.shape[1], gs.data_ptr() if gs is not None else None, q_out.data_ptr() + col0 // 2, q_out.stride(0),
-            sf_out.data_ptr(), sf_cols, sf_layout, col0 // group, rows, cols, _lib.QUANT_ROUND_BF16 if round_bf16 else 0,
-            _stream(x))
+            sf_out.data_ptr(), sf_cols, sf_layout, col0 // group, row_scale.data_ptr() if row_scale is not None else None,
+            col_scale.data_ptr() if col_scale is not None else None, rows, cols,
+            _lib.QUANT_ROUND_BF16 if round_bf16 else 0, _stream(x))
     _lib.check(rc, "wush_fused_quantize_strided")
+
+
+def row_sumsq(x: torch.Tensor) -> torch.Tensor:
+    """fp32 [rows]: sum of squares of every row of a bf16 matrix (rows may be strided)."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise ValueError("x must be a 2-D bfloat16 tensor with unit column stride")
+    out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().wush_row_sumsq(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], _stream(x))
+    _lib.check(rc, "wush_row_sumsq")
+    return out
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """bf16(silu(gate)) * up for two bf16 [rows, cols] tensors with a common row stride (e.g. column halves of one
+    fused projection output)."""
+    _require_cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.dim() != 2 \
+            or gate.stride() != up.stride() or gate.stride(1) != 1:
+        raise ValueError("gate and up must be bfloat16 [rows, cols] tensors with the same strides")
+    out = torch.empty(gate.shape, dtype=torch.bfloat16, device=gate.device)
+    with torch.cuda.device(gate.device):
+        rc = _lib.load().wush_swiglu(gate.data_ptr(), up.data_ptr(), gate.stride(0), out.data_ptr(), out.stride(0),
+                                     gate.shape[0], gate.shape[1], _stream(gate))
+    _lib.check(rc, "wush_swiglu")
+    return out
 
 
 # --------------------------------------------------------------------------------------------
