@@ -221,8 +221,12 @@ WUSH_API int wush_hessian_tile_coords(int64_t hidden, int64_t tile, int* row_blo
 WUSH_API int wush_hessian_accumulate_tiles(float* h, const void* x, int64_t tokens, int64_t hidden, int64_t tile_begin,
                                            int64_t tile_end, int flags, int* status, void* stream);
 
-/* Writes the mirror image (upper triangle) of the tiles [tile_begin, tile_end) from their lower-triangle values. */
-WUSH_API int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream);
+/*
+ * Writes the mirror image (upper triangle) of the tiles [tile_begin, tile_end) from their lower-triangle values.
+ * barrier_slots / barrier_epoch / rank / world: as for wush_hessian_peer_reduce (NULL slots: no barrier).
+ */
+WUSH_API int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, int rank, int world,
+                                       uint32_t* const* barrier_slots, uint32_t barrier_epoch, int* status, void* stream);
 
 /*
  * h[i][j] <- scale * h[i][j] for j <= i, and h[j][i] <- the same value: turns a lower-triangular raw sum
@@ -248,12 +252,20 @@ WUSH_API int wush_hessian_finalize_count(float* h, int64_t hidden, const int64_t
  * The 32 x 32 sub-tiles of the range are dealt round-robin to the ranks.  On return (stream order) every
  * rank's buffer holds, for the sub-tiles this rank owns, the sum over ranks divided by the total token count
  * (lower triangle only; wush_hessian_mirror_tiles rebuilds the rest locally).  Once EVERY rank has run it, all
- * buffers hold the same bits for the range.  The caller separates the launches from the producers and consumers
- * of the range with cross-rank barriers: all ranks' partial sums of the range complete before any rank starts,
- * all ranks done before the result is read.  hidden % 4 == 0, world <= 16.
+ * buffers hold the same bits for the range.  The launches must be separated from the producers and consumers of
+ * the range by cross-rank barriers: all ranks' partial sums of the range complete before any rank starts, all
+ * ranks done before the result is read.  hidden % 4 == 0, world <= 16.
+ *   barrier_slots  NULL: the caller runs those barriers.  Otherwise a DEVICE array of `world` pointers to every
+ *           rank's array of 16 uint32 slots in peer-addressable memory (zero before the first use): the kernel then
+ *           starts with a barrier of its own -- it stores barrier_epoch into its slot on every rank and waits until
+ *           all of its own slots have reached it -- which says "the previous kernel of my stream is complete" to
+ *           the other ranks at the cost of one NVLink round trip instead of a separate barrier kernel.  Every use
+ *           (of this call or of wush_hessian_mirror_tiles) on the same slots takes the next barrier_epoch, the
+ *           same on all ranks.  The wait is bounded; on expiry *status (DEVICE int, may be NULL) is set to 1.
  */
 WUSH_API int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const int64_t* const* counts, int rank,
-                                      int world, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream);
+                                      int world, int64_t hidden, int64_t tile_begin, int64_t tile_end,
+                                      uint32_t* const* barrier_slots, uint32_t barrier_epoch, int* status, void* stream);
 
 /*
  * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.

@@ -64,12 +64,13 @@ def test_update_staging_matches_direct_launches():
     assert np.linalg.norm(hf - w3) <= 2e-3 * np.linalg.norm(w3)
 
 
-def _worker(rank, world, port, out, peer, multimem, per_panel, tokens0):
+def _worker(rank, world, port, out, peer, multimem, per_panel, tokens0, kernel_barrier):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
                       WUSH_B200_HESSIAN_PEER="1" if peer else "0", WUSH_B200_HESSIAN_MULTIMEM="1" if multimem else "0",
-                      WUSH_B200_HESSIAN_TILES_PER_PANEL=str(per_panel))
+                      WUSH_B200_HESSIAN_TILES_PER_PANEL=str(per_panel),
+                      WUSH_B200_HESSIAN_KERNEL_BARRIER="1" if kernel_barrier else "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -115,16 +116,18 @@ def _worker(rank, world, port, out, peer, multimem, per_panel, tokens0):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("peer,multimem,per_panel,tokens0", [(True, True, 0, 1024), (True, False, 3, 1024), (True, True, 4, 50000),
-                                                             (False, False, 0, 1024)])
-def test_two_gpu_hessian(tmp_path, peer, multimem, per_panel, tokens0):
+@pytest.mark.parametrize("peer,multimem,per_panel,tokens0,kernel_barrier",
+                         [(True, True, 0, 1024, True), (True, False, 3, 1024, True), (True, True, 4, 50000, True),
+                          (True, True, 3, 1024, False), (False, False, 0, 1024, True)])
+def test_two_gpu_hessian(tmp_path, peer, multimem, per_panel, tokens0, kernel_barrier):
     """peer=True: ranks combined by the reduce kernel over NVLink (multimem: sums formed inside the NVSwitch when
     a multicast address is available; per_panel > 0: the tile list is combined in several overlapped panels;
-    50000 tokens: two 32768-token segments per rank); peer=False: NCCL all-reduce of row panels."""
+    50000 tokens: two 32768-token segments per rank; kernel_barrier: the reduce and mirror kernels run the cross-rank
+    barriers themselves instead of separate barrier kernels); peer=False: NCCL all-reduce of row panels."""
     import torch.multiprocessing as mp
     out = str(tmp_path / "h.npy")
-    port = 29650 + os.getpid() % 300 + 7 * per_panel + (3 if multimem else 0)
-    mp.spawn(_worker, args=(2, port, out, peer, multimem, per_panel, tokens0), nprocs=2, join=True)
+    port = 29650 + os.getpid() % 300 + 7 * per_panel + (3 if multimem else 0) + (1 if kernel_barrier else 0)
+    mp.spawn(_worker, args=(2, port, out, peer, multimem, per_panel, tokens0, kernel_barrier), nprocs=2, join=True)
     got = np.load(out).astype(np.float64)
     want = wo.wush_update_sequence([synth.bf16_to_f64(synth.activations(tokens0 + 256 * r, 1024, seed=70 + r)) for r in range(2)])
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()

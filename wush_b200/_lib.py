@@ -66,9 +66,9 @@ def load() -> ctypes.CDLL:
         "wush_hessian_accumulate_rows": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
         "wush_hessian_finalize": [vp, i64, ctypes.c_float, vp],
         "wush_hessian_finalize_count": [vp, i64, vp, vp],
-        "wush_hessian_peer_reduce": [vp, vp, vp, i32, i32, i64, i64, i64, vp],
+        "wush_hessian_peer_reduce": [vp, vp, vp, i32, i32, i64, i64, i64, vp, ctypes.c_uint32, vp, vp],
         "wush_hessian_accumulate_tiles": [vp, vp, i64, i64, i64, i64, i32, vp, vp],
-        "wush_hessian_mirror_tiles": [vp, i64, i64, i64, vp],
+        "wush_hessian_mirror_tiles": [vp, i64, i64, i64, i32, i32, vp, ctypes.c_uint32, vp, vp],
         "wush_hessian_tiles_per_wave": [],
         "wush_hessian_tile_coords": [i64, i64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
         "wush_gemm_cluster_capacity": [i32, i32],

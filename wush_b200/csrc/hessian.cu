@@ -689,32 +689,6 @@ __global__ void finalize_kernel(float* __restrict__ h, int64_t hidden, float sca
   }
 }
 
-// Mirror image of entries [tile_begin, tile_end) of the 256 x 256 tile list: a block copies one 32 x 32
-// sub-tile of the lower triangle to its transposed place.  Sub-tiles above the diagonal of a diagonal tile
-// are skipped, diagonal sub-tiles mirror their strictly lower part.
-__global__ void mirror_tiles_kernel(float* __restrict__ h, int64_t hidden, int nblk, int64_t tile_begin, int64_t n_items) {
-  __shared__ float tile[32][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (int64_t k = blockIdx.x; k < n_items; k += gridDim.x) {
-    int bi, bj;
-    pair_tile_coords(tile_begin + (k >> 6), 0, nblk, bi, bj);
-    const int sub = (int)(k & 63);
-    const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);   // 32 x 32 sub-tile (si, sj)
-    if (sj > si) continue;                                                             // uniform per block
-#pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-      const int64_t i = si * 32 + r, j = sj * 32 + tx;
-      tile[r][tx] = (i < hidden && j < hidden && j <= i) ? h[i * hidden + j] : 0.0f;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-      const int64_t jr = sj * 32 + r, ic = si * 32 + tx;
-      if (jr < hidden && ic < hidden && jr < ic) h[jr * hidden + ic] = tile[tx][r];
-    }
-    __syncthreads();
-  }
-}
 }  // namespace hess
 }  // namespace wush
 
@@ -745,20 +719,6 @@ extern "C" int wush_hessian_accumulate_tiles(float* h, const void* x, int64_t to
                                              int64_t tile_end, int flags, int* status, void* stream) {
   if (tile_begin < 0) return WUSH_ERR_BAD_SHAPE;
   return hessian_launch(h, x, tokens, hidden, 0, hidden, tile_begin, tile_end, flags, status, (cudaStream_t)stream);
-}
-
-extern "C" int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream) {
-  if (!h) return WUSH_ERR_NULL_POINTER;
-  if (hidden <= 0 || tile_begin < 0 || tile_end < tile_begin || tile_end > wush_hessian_tile_count(hidden))
-    return WUSH_ERR_BAD_SHAPE;
-  const int64_t items = (tile_end - tile_begin) * 64;
-  if (items == 0) return WUSH_OK;
-  int64_t blocks = items;
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  hess::mirror_tiles_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(h, hidden, (int)((hidden + 255) / 256),
-                                                                               tile_begin, items);
-  return (int)cudaGetLastError();
 }
 
 static int hessian_finalize(float* h, int64_t hidden, float scale, const long long* count, void* stream);

@@ -13,8 +13,10 @@
 //              multimem.st (the switch replicates it): a rank pulls and pushes 1/W of the range, its links
 //              carry about half of what the plain exchange needs.
 // Only the lower triangle travels; every rank rebuilds the mirror image locally at HBM speed
-// (wush_hessian_mirror_tiles).  The caller brackets the launch with two cross-rank barriers (the partial sums
-// of the range are complete everywhere before / every rank has delivered after).  Because the kernel works
+// (wush_hessian_mirror_tiles).  The launch must be bracketed by two cross-rank barriers (the partial sums of the
+// range are complete everywhere before / every rank has delivered after).  Both kernels can run the barrier that
+// precedes them themselves (cross_rank_arrive_and_wait below): a separate barrier kernel costs 10-15 us, more
+// than the exchange of a small range itself.  Because the kernel works
 // on tile ranges, finished ranges can be combined while the accumulation kernel is still busy with later
 // tiles: it is small enough (256 threads, 40 registers, 4 KB of shared memory) to be co-resident with it.
 // No TMA, no cluster multicast: 16-byte loads and stores on peer or multicast addresses.
@@ -30,6 +32,38 @@ namespace peer {
 
 constexpr int kMaxWorld = 16;
 
+// In-kernel barrier across the ranks, run at the start of a kernel.  Every rank owns `kMaxWorld` 32-bit slots in
+// peer-addressable memory; slot s of rank r is written only by rank s.  A use of the barrier has a number (`epoch`,
+// the same on all ranks, growing by one per use): the first thread of the grid's first block stores it into its
+// slot on every rank, and every block waits until all of its own rank's slots have reached it.  What the previous
+// kernel of the stream wrote (locally or into peer memory) is complete when this kernel starts, so a rank's arrival
+// says "my previous kernel is done".  The wait is bounded; on expiry the status word is set and the kernel goes on.
+struct RankBarrier {
+  uint32_t* const* slots;          // device array [world]: every rank's slot array (null: the caller synchronises)
+  uint32_t epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void cross_rank_arrive_and_wait(const RankBarrier& b, int rank, int world) {
+  if (b.slots == nullptr) return;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    uint32_t* dst = b.slots[threadIdx.x] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(dst), "r"(b.epoch) : "memory");
+  }
+  if (threadIdx.x < world) {
+    const uint32_t* mine = b.slots[rank] + threadIdx.x;
+    uint32_t seen = 0;
+    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {      // seconds: far beyond any skew between the ranks
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(mine) : "memory");
+      if ((int32_t)(seen - b.epoch) >= 0) break;
+      __nanosleep(64);
+    }
+    if ((int32_t)(seen - b.epoch) < 0 && b.status) atomicExch(b.status, 1);
+  }
+  __syncthreads();
+}
+
 struct Params {
   float* const* bufs;              // device array [world]: base of every rank's H buffer
   float* mc;                       // multicast address of the same buffer (multimem variant), else null
@@ -40,6 +74,7 @@ struct Params {
   int64_t tile_begin;
   int64_t n_items;                 // (tiles in range) * (sub-tiles per tile owned by this rank)
   int per_tile;                    // sub-tiles of one tile owned by this rank
+  RankBarrier barrier;
 };
 
 __device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc_addr) {
@@ -59,15 +94,16 @@ __device__ __forceinline__ void multimem_st(float* mc_addr, const float4& v) {
 template <bool MC>
 __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
   __shared__ float* s_bufs[kMaxWorld];
-  __shared__ float s_scale;
-  if (threadIdx.x < p.world) s_bufs[threadIdx.x] = p.bufs[(threadIdx.x + p.rank) % p.world];   // own buffer first
-  if (threadIdx.x == 0) {
-    long long total = 0;
-    for (int r = 0; r < p.world; ++r) total += *p.counts[r];
-    s_scale = 1.0f / (float)(total > 0 ? total : 1);
+  __shared__ long long s_counts[kMaxWorld];
+  cross_rank_arrive_and_wait(p.barrier, p.rank, p.world);
+  if (threadIdx.x < p.world) {
+    s_bufs[threadIdx.x] = p.bufs[(threadIdx.x + p.rank) % p.world];   // own buffer first
+    s_counts[threadIdx.x] = *p.counts[threadIdx.x];                    // the peers' counts in parallel
   }
   __syncthreads();
-  const float scale = s_scale;
+  long long total = 0;
+  for (int r = 0; r < p.world; ++r) total += s_counts[r];
+  const float scale = 1.0f / (float)(total > 0 ? total : 1);
   const int row_in = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;   // this thread's float4 inside a sub-tile
 
   for (int64_t k = blockIdx.x; k < p.n_items; k += gridDim.x) {
@@ -105,7 +141,9 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
 }  // namespace wush
 
 extern "C" int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const int64_t* const* counts, int rank,
-                                        int world, int64_t hidden, int64_t tile_begin, int64_t tile_end, void* stream) {
+                                        int world, int64_t hidden, int64_t tile_begin, int64_t tile_end,
+                                        uint32_t* const* barrier_slots, uint32_t barrier_epoch, int* status,
+                                        void* stream) {
   using namespace wush;
   if (!bufs || !counts) return WUSH_ERR_NULL_POINTER;
   if (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world) return WUSH_ERR_BAD_SHAPE;
@@ -114,16 +152,68 @@ extern "C" int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const
   if (tile_begin < 0 || tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk)) return WUSH_ERR_BAD_SHAPE;
   if (mc_buf && ((uintptr_t)mc_buf & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   peer::Params p{bufs, mc_buf, reinterpret_cast<const long long* const*>(counts), rank, world, hidden, nblk,
-                 tile_begin, 0, 0};
+                 tile_begin, 0, 0, {barrier_slots, barrier_epoch, status}};
   p.per_tile = rank < 64 ? (64 - rank + world - 1) / world : 0;
   p.n_items = (tile_end - tile_begin) * p.per_tile;
-  if (p.n_items <= 0) return WUSH_OK;
-  int64_t blocks = p.n_items;
+  if (p.n_items <= 0 && barrier_slots == nullptr) return WUSH_OK;
+  int64_t blocks = p.n_items > 0 ? p.n_items : 1;       // an empty range still takes part in the barrier
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (mc_buf)
     peer::peer_reduce_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
   else
     peer::peer_reduce_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// ---- mirror image of a tile range, optionally behind the in-kernel barrier ------------------------------------
+namespace wush {
+namespace peer {
+
+// A block copies 32 x 32 sub-tiles of the lower triangle to their transposed places.  Sub-tiles above the diagonal
+// of a diagonal tile are skipped, diagonal sub-tiles mirror their strictly lower part.
+__global__ void __launch_bounds__(256) mirror_tiles_kernel(float* __restrict__ h, int64_t hidden, int nblk, int64_t tile_begin,
+                                                           int64_t n_items, int rank, int world, const RankBarrier barrier) {
+  __shared__ float tile[32][33];
+  cross_rank_arrive_and_wait(barrier, rank, world);
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int64_t k = blockIdx.x; k < n_items; k += gridDim.x) {
+    int bi, bj;
+    hess::pair_tile_coords(tile_begin + (k >> 6), 0, nblk, bi, bj);
+    const int sub = (int)(k & 63);
+    const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);   // 32 x 32 sub-tile (si, sj)
+    if (sj > si) continue;                                                             // uniform per block
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t i = si * 32 + r, j = sj * 32 + tx;
+      tile[r][tx] = (i < hidden && j < hidden && j <= i) ? h[i * hidden + j] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t jr = sj * 32 + r, ic = si * 32 + tx;
+      if (jr < hidden && ic < hidden && jr < ic) h[jr * hidden + ic] = tile[tx][r];
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace peer
+}  // namespace wush
+
+extern "C" int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_begin, int64_t tile_end, int rank, int world,
+                                         uint32_t* const* barrier_slots, uint32_t barrier_epoch, int* status, void* stream) {
+  using namespace wush;
+  if (!h) return WUSH_ERR_NULL_POINTER;
+  const int nblk = (int)((hidden + 255) / 256);
+  if (hidden <= 0 || tile_begin < 0 || tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk)) return WUSH_ERR_BAD_SHAPE;
+  if (barrier_slots && (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world)) return WUSH_ERR_BAD_SHAPE;
+  const int64_t items = (tile_end - tile_begin) * 64;
+  if (items == 0 && barrier_slots == nullptr) return WUSH_OK;
+  int64_t blocks = items > 0 ? items : 1;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  peer::mirror_tiles_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      h, hidden, nblk, tile_begin, items, rank, world, peer::RankBarrier{barrier_slots, barrier_epoch, status});
   return (int)cudaGetLastError();
 }

@@ -137,7 +137,8 @@ class _PeerBuffers:
         import torch.distributed._symmetric_memory as symm
         grp = group if group is not None else dist.group.WORLD
         n = hidden * hidden
-        self.flat = symm.empty(n + 4, dtype=torch.float32, device=device)      # 16 spare bytes: int64 token count
+        # behind the matrix: the int64 token count (16 bytes) and 16 uint32 slots of the in-kernel barrier
+        self.flat = symm.empty(n + 4 + 16, dtype=torch.float32, device=device)
         self.handle = symm.rendezvous(self.flat, group=grp)
         self.h = self.flat[:n].view(hidden, hidden)
         self.count = self.flat[n:n + 2].view(torch.int64)
@@ -145,6 +146,12 @@ class _PeerBuffers:
         self.rank, self.world = self.handle.rank, self.handle.world_size
         self.buf_table = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.count_table = torch.tensor([x + 4 * n for x in ptrs], dtype=torch.int64, device=device)
+        self.slot_table = torch.tensor([x + 4 * (n + 4) for x in ptrs], dtype=torch.int64, device=device)
+        self.flat[n + 4:].zero_()
+        torch.cuda.synchronize(device)
+        self.handle.barrier(channel=0)            # nobody signals before every rank's slots are zero
+        self.epoch = 0
+        self.kernel_barrier = os.environ.get("WUSH_B200_HESSIAN_KERNEL_BARRIER", "1") != "0"
         self.mc_ptr = 0
         if os.environ.get("WUSH_B200_HESSIAN_MULTIMEM", "1") != "0":
             try:
@@ -167,18 +174,27 @@ class _PeerBuffers:
     def combine(self, hidden: int, tile_begin: int, tile_end: int, channel: int) -> None:
         """On the current stream: wait until every rank's partial sums of the tile range are complete, sum them
         across the ranks (scaled by 1 / total tokens), wait until every rank has delivered, rebuild the mirror
-        image of the range locally."""
+        image of the range locally.  The two waits are barriers the reduce and the mirror kernel run themselves
+        (WUSH_B200_HESSIAN_KERNEL_BARRIER=0: separate symmetric-memory barrier kernels on `channel`)."""
         lib = _lib.load()
         dev = self.flat.device
         stream = torch.cuda.current_stream(dev).cuda_stream
-        self.handle.barrier(channel=channel)
+        status = _lib.status_word(dev).data_ptr()
+        slots = self.slot_table.data_ptr() if self.kernel_barrier else None
+        if not self.kernel_barrier:
+            self.handle.barrier(channel=channel)
+        self.epoch += 1
         with torch.cuda.device(dev):
             rc = lib.wush_hessian_peer_reduce(self.buf_table.data_ptr(), self.mc_ptr or None, self.count_table.data_ptr(),
-                                              self.rank, self.world, hidden, tile_begin, tile_end, stream)
+                                              self.rank, self.world, hidden, tile_begin, tile_end, slots, self.epoch,
+                                              status, stream)
         _lib.check(rc, "wush_hessian_peer_reduce")
-        self.handle.barrier(channel=channel)
+        if not self.kernel_barrier:
+            self.handle.barrier(channel=channel)
+        self.epoch += 1
         with torch.cuda.device(dev):
-            rc = lib.wush_hessian_mirror_tiles(self.h.data_ptr(), hidden, tile_begin, tile_end, stream)
+            rc = lib.wush_hessian_mirror_tiles(self.h.data_ptr(), hidden, tile_begin, tile_end, self.rank, self.world,
+                                               slots, self.epoch, status, stream)
         _lib.check(rc, "wush_hessian_mirror_tiles")
 
 
