@@ -176,23 +176,29 @@ __global__ void __launch_bounds__(256) mirror_tiles_kernel(float* __restrict__ h
                                                            int64_t n_items, int rank, int world, const RankBarrier barrier) {
   __shared__ float tile[32][33];
   cross_rank_arrive_and_wait(barrier, rank, world);
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int row = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;       // this thread's 16 bytes of a 32 x 32 sub-tile
   for (int64_t k = blockIdx.x; k < n_items; k += gridDim.x) {
     int bi, bj;
     hess::pair_tile_coords(tile_begin + (k >> 6), 0, nblk, bi, bj);
     const int sub = (int)(k & 63);
     const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);   // 32 x 32 sub-tile (si, sj)
     if (sj > si) continue;                                                             // uniform per block
-#pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-      const int64_t i = si * 32 + r, j = sj * 32 + tx;
-      tile[r][tx] = (i < hidden && j < hidden && j <= i) ? h[i * hidden + j] : 0.0f;
-    }
+    const int64_t i = si * 32 + row, j = sj * 32 + c4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < hidden && j < hidden) v = *reinterpret_cast<const float4*>(h + i * hidden + j);   // hidden % 4 == 0
+    tile[row][c4] = v.x; tile[row][c4 + 1] = v.y; tile[row][c4 + 2] = v.z; tile[row][c4 + 3] = v.w;
     __syncthreads();
+    // row `row` of the transposed sub-tile, columns c4 .. c4 + 3: elements (sj*32 + row, si*32 + c4 + u)
+    const int64_t jr = sj * 32 + row, ic = si * 32 + c4;
+    if (jr < hidden && ic < hidden) {
+      if (si != sj) {
+        *reinterpret_cast<float4*>(h + jr * hidden + ic) = make_float4(tile[c4][row], tile[c4 + 1][row], tile[c4 + 2][row], tile[c4 + 3][row]);
+      } else {
+        // diagonal sub-tile: only the strictly upper part is a mirror image
 #pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-      const int64_t jr = sj * 32 + r, ic = si * 32 + tx;
-      if (jr < hidden && ic < hidden && jr < ic) h[jr * hidden + ic] = tile[tx][r];
+        for (int u = 0; u < 4; ++u)
+          if (jr < ic + u) h[jr * hidden + ic + u] = tile[c4 + u][row];
+      }
     }
     __syncthreads();
   }
@@ -206,7 +212,9 @@ extern "C" int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_
   using namespace wush;
   if (!h) return WUSH_ERR_NULL_POINTER;
   const int nblk = (int)((hidden + 255) / 256);
-  if (hidden <= 0 || tile_begin < 0 || tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk)) return WUSH_ERR_BAD_SHAPE;
+  if (hidden <= 0 || hidden % 4 != 0 || tile_begin < 0 || tile_end < tile_begin || tile_end > hess::pair_tile_count(nblk))
+    return WUSH_ERR_BAD_SHAPE;
+  if ((uintptr_t)h & 15) return WUSH_ERR_BAD_ALIGNMENT;
   if (barrier_slots && (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world)) return WUSH_ERR_BAD_SHAPE;
   const int64_t items = (tile_end - tile_begin) * 64;
   if (items == 0 && barrier_slots == nullptr) return WUSH_OK;

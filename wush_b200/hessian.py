@@ -103,20 +103,32 @@ def token_segments(tokens: int) -> list[tuple[int, int]]:
     return out
 
 
-def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 4) -> list[tuple[int, int]]:
+def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 5, ratio: float = 3.0) -> list[tuple[int, int]]:
     """Cut the tile list [0, n_tiles) into launches whose cross-GPU combine can overlap the next launch.
 
     A launch works on `per_wave` tiles side by side, so a launch over a multiple of per_wave tiles wastes
     nothing.  The last panel is the (possibly partly filled) last wave: its combine is the only one nothing
-    hides, so it is kept as small as the tile count allows; the full waves before it are cut into up to
-    max_panels - 1 panels of whole waves."""
+    hides, so it is kept as small as the tile count allows.  The combine of a panel runs while the NEXT panel is
+    multiplied and costs a fraction of the panel's own multiply time per tile, so the panels before the last shrink
+    geometrically towards the end (each about `ratio` times the next, whole waves): one wave before the last, then
+    about three, nine, ... and the first panel takes what is left."""
     per_wave = max(1, per_wave)
     waves = -(-n_tiles // per_wave)
     if waves <= 1 or max_panels <= 1:
         return [(0, n_tiles)] if n_tiles else []
-    head = waves - 1
-    k = min(max_panels - 1, head)
-    cuts = sorted({round(head * i / k) * per_wave for i in range(k + 1)})
+    head = waves - 1                                   # full waves before the last one
+    sizes, size = [], 1.0
+    while head > 0 and len(sizes) < max_panels - 2:
+        take = min(head, max(1, int(round(size))))
+        sizes.append(take)
+        head -= take
+        size *= ratio
+    if head > 0:
+        sizes.append(head)
+    sizes.reverse()
+    cuts = [0]
+    for w in sizes:
+        cuts.append(cuts[-1] + w * per_wave)
     return [(a, b) for a, b in zip(cuts[:-1], cuts[1:])] + [(cuts[-1], n_tiles)]
 
 
@@ -228,7 +240,7 @@ class DistributedHessian:
     (gloo) with a stand-in for the CUDA kernels; the defaults call the kernels and need a GPU.
     """
 
-    def __init__(self, hidden: int, device, group=None, panels: int = 4, accumulate_fn=None, finalize_fn=None,
+    def __init__(self, hidden: int, device, group=None, panels: int = 5, accumulate_fn=None, finalize_fn=None,
                  peer: bool | None = None, stage_tokens: int | None = None):
         import os
         import torch.distributed as dist
