@@ -138,3 +138,51 @@ def test_prepare_kernel_matches_torch_linear_algebra(fmt):
     assert float((qt @ qt.transpose(-2, -1) - eye).abs().max()) < 1e-12
     assert float((qt @ mm - rn).abs().max()) < 1e-11 * float(mm.abs().max())
     assert float(rn.tril(-1).abs().max()) == 0.0
+
+
+def _row_shard_worker(rank, world, port, out, rtn):
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from wush_b200 import gptq
+    w, h = _row_shard_inputs()
+    rows = w.shape[0] // world
+    res = gptq.gptq_babai_sweep(w[rank * rows:(rank + 1) * rows].to(dev), h.to(dev), "mxfp4", "wush", force_rtn=rtn,
+                                group=dist.group.WORLD, total_rows=w.shape[0])
+    torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in res.items()}, f"{out}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _row_shard_inputs():
+    x = synth.bf16_to_f64(synth.activations(2048, 256, seed=21))
+    h = torch.from_numpy((x.T @ x / x.shape[0]).astype(np.float32))
+    return synth.weights(512, 256, seed=22), h
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("rtn", [True, False])
+def test_row_sharded_sweep_on_two_gpus_matches_the_unsharded_sweep(tmp_path, rtn):
+    """Weight rows split over two GPUs; only the G x G Gram matrices of the block targets are all-reduced.  The
+    transforms (same on both ranks) and each rank's codes and scales must be those of the sweep of the whole matrix
+    (float64 summation order differs, which can flip a rounding-boundary case)."""
+    import os
+    import torch.multiprocessing as mp
+    from wush_b200 import gptq
+    out = str(tmp_path / "s")
+    mp.spawn(_row_shard_worker, args=(2, 29400 + os.getpid() % 300 + int(rtn), out, rtn), nprocs=2, join=True)
+    parts = [torch.load(f"{out}.{r}", weights_only=False) for r in range(2)]
+    dev = torch.device("cuda:0")
+    w, h = _row_shard_inputs()
+    whole = gptq.gptq_babai_sweep(w.to(dev), h.to(dev), "mxfp4", "wush", force_rtn=rtn)
+    assert torch.equal(parts[0]["transform_basis"], parts[1]["transform_basis"])
+    assert float((parts[0]["transform_basis"].float() != whole["transform_basis"].cpu().float()).float().mean()) <= 1e-3
+    codes = torch.cat([p["qweight"] for p in parts])
+    scales = torch.cat([p["scale_quant"].view(torch.uint8) for p in parts])
+    assert float((scales != whole["scale_quant"].view(torch.uint8).cpu()).float().mean()) <= 1e-3
+    assert float((codes != whole["qweight"].cpu()).float().mean()) <= 2e-3

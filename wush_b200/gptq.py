@@ -112,7 +112,8 @@ def _block_step(rn, y, qt, tmat, nblocks, col_block0, rows, codes, scales, fake,
 
 @torch.no_grad()
 def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_type: str, transform_class: str,
-                     force_rtn: bool = False, transforms: torch.Tensor | None = None) -> dict:
+                     force_rtn: bool = False, transforms: torch.Tensor | None = None, group=None,
+                     total_rows: int | None = None) -> dict:
     """Quantize one (concatenated) weight matrix: the work of gptq_babai_outer as quantize_layers drives it
     (wush_gptq.py:373-441: block size = group size, `force_rtn` for the outer and the inner loop, transforms
     rounded to the weight dtype).
@@ -125,6 +126,12 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
     Per block the GPU runs: the Gram matrix of the targets (cuBLAS), `wush_gptq_block_prepare` (transform, QR),
     `wush_gptq_block_step` (everything per weight row) and the update of the remaining targets (cuBLAS) --
     four launches and no host synchronisation; round-to-nearest mode does all blocks with one launch of each.
+
+    Row-sharded over GPUs (`group` given, `total_rows` = rows of the whole matrix): every rank passes ITS rows of
+    the weight and the same Hessian.  The sweep is independent per weight row except for the block transforms,
+    which depend on the Gram matrix of the targets of ALL rows: the per-rank G x G Gram matrices are summed with one
+    all-reduce per block (one for all blocks in round-to-nearest mode) and everything else stays local, so every
+    rank computes the same transforms and its own rows' codes; the results are the rows of the unsharded sweep.
     """
     if not weight.is_cuda:
         raise RuntimeError("wush_b200 runs on CUDA devices only")
@@ -137,6 +144,17 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
     rows, cols = weight.shape
     if cols % g:
         raise ValueError(f"in_features must be a multiple of {g}")
+    sharded = group is not None or total_rows is not None
+    if sharded:
+        import torch.distributed as dist
+        if total_rows is None:
+            raise ValueError("a row-sharded sweep needs total_rows (the R^-1/2 factor of the transform uses all rows)")
+    all_rows = total_rows if sharded else rows
+
+    def all_ranks(gram_t):
+        if sharded and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(gram_t, group=group)
+        return gram_t
     dev, nb = weight.device, cols // g
     f32 = weight.dtype == torch.float32
     x = weight.t().to(torch.float64).contiguous()                                     # (C, R), :188
@@ -161,9 +179,9 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
         idx = torch.arange(nb, device=dev)
         basis = u.view(nb, g, nb, g)[idx, :, idx, :].contiguous()                     # (nb, G, G) diagonal blocks
         yb = basis @ x.view(nb, g, rows)
-        gram = yb @ yb.transpose(-2, -1) if need_gram else None
+        gram = all_ranks(yb @ yb.transpose(-2, -1)) if need_gram else None
         rn, qt = torch.empty_like(tb), torch.empty_like(tb)
-        _prepare(gram, basis, g, g * g, nb, fmt, transform, f32, rows, tb, rn, qt, status)
+        _prepare(gram, basis, g, g * g, nb, fmt, transform, f32, all_rows, tb, rn, qt, status)
         _block_step(rn, yb, qt, tb, nb, 0, rows, codes, scales, fake, None, fmt, True)
     else:
         y = u @ x                                                                     # :210
@@ -175,7 +193,8 @@ def gptq_babai_sweep(weight: torch.Tensor, hessian: torch.Tensor | None, quant_t
             yb = y[i1:i2]
             if need_gram:
                 torch.mm(yb, yb.t(), out=gram)
-            _prepare(gram, u[i1:i2, i1:i2], cols, diag_step, 1, fmt, transform, f32, rows, tb[b], rn, qt, status)
+                all_ranks(gram)
+            _prepare(gram, u[i1:i2, i1:i2], cols, diag_step, 1, fmt, transform, f32, all_rows, tb[b], rn, qt, status)
             # the coefficients go straight into x (:221), which the update of the remaining targets reads (:222)
             _block_step(rn, yb, qt, tb[b], 1, b, rows, codes, scales, fake, x[i1:i2], fmt, False)
             if i1:
