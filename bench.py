@@ -627,6 +627,80 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
             "clocks": clocks.summary()}
 
 
+def bench_layer_4096(args, dev, torch) -> dict:
+    """The reference's CPU-runnable case on the GPU: one 4096 x 4096 layer, second moment from 16 x 2048 calibration
+    tokens, MXFP4 round-to-nearest sweep with WUSH transforms, then the real-quant forward of 2048 tokens (fused
+    transform + quantize, FP4 GEMM).  Next to it the CPU pseudo-quantizer (the oracle) on a bounded sample: the sweep
+    of 64 weight rows and the activation quantizer + float64 product for the same 64 output features, whose result
+    is also the parity check of the GPU layer."""
+    import numpy as np
+    from oracle import synth
+    from oracle import wush_oracle as wo
+    from wush_b200 import gptq
+    from wush_b200.hessian import DistributedHessian
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    hidden, tokens = 4096, 2048
+    calib = [synth.activations(2048, hidden, seed=500 + i).to(dev) for i in range(16)]
+    w = synth.weights(hidden, hidden, seed=520)
+    x = synth.activations(tokens, hidden, seed=530)
+    wd, xd = w.to(dev), x.to(dev)
+
+    def calibrate():
+        dh = DistributedHessian(hidden, dev, peer=False)
+        for c in calib:
+            dh.update(c[None])
+        return dh.finalize()
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            out = fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1e3 / reps, out
+
+    with ClockSampler(dev.index) as clocks:
+        t_h, h = timed(calibrate, 3)
+        t_s, res = timed(lambda: gptq.gptq_babai_sweep(wd, h, "mxfp4", "wush", force_rtn=True), 3)
+        entry = gptq.export_realquant({k: res[k] for k in ("transform_basis", "qweight", "scale_quant", "global_scale")}, "mxfp4")
+        layer = FPQuantLinear(hidden, hidden, FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, transform_init="wush"),
+                              bias=False, device=dev)
+        layer.load_quantized(entry["qweight"], entry["scales"], entry["forward_hadamard_matrix"],
+                             entry["weight_global_scale"], entry["act_global_scale"])
+        y = layer(xd)
+        t_f = _time_steps(lambda: layer(xd), 20, torch, graph=True)
+    # ---- CPU pseudo-quantizer on a sample, same transforms -------------------------------------------------
+    rows = np.sort(np.random.default_rng(0).choice(hidden, size=64, replace=False))
+    t = res["transform_basis"].double().cpu().numpy()
+    h64 = h.double().cpu().numpy()
+    t0 = time.perf_counter()
+    ref_w = wo.gptq_babai_outer(synth.bf16_to_f64(w)[rows], h64, "mxfp4", "wush", True, transform_fn=lambda b, basis, yy: t[b])
+    cpu_sweep = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    ref_x = wo.fused_transform_quant(synth.bf16_to_f64(x), wo.transform_to_matrix(t), "mxfp4")["fake_quant"]
+    want = ref_x @ ref_w["fake_quant"].T
+    cpu_fwd = time.perf_counter() - t0
+    got = y.double().cpu().numpy()[:, rows]
+    rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    code_bad = float(np.mean(wo.unpack_e2m1_codes(res["qweight"].cpu().numpy()[rows]) != ref_w["codes"]))
+    scale_ok = bool(np.array_equal(res["scale_quant"].view(torch.uint8).cpu().numpy()[rows], ref_w["scale_quant"]))
+    par = _parity("layer_4096", rel if scale_ok and code_bad <= 1e-3 else float("inf"), 1e-2,
+                  "relative Frobenius error of 2048 x 64 sampled outputs of the real-quant layer vs the CPU pseudo-quantizer "
+                  "(oracle sweep + oracle activation quantizer + float64 product); weight scale bytes identical, codes "
+                  f"differing on {code_bad:.1e} of the sampled elements")
+    return {"metric": "layer_4096_quantize_and_forward_ms", "value": t_h + t_s + t_f, "unit": "ms", "ms_per_step": t_h + t_s + t_f,
+            "hessian_ms": t_h, "sweep_ms": t_s, "forward_ms": t_f,
+            "forward_TFLOPS": 2.0 * tokens * hidden * hidden / (t_f * 1e-3) / 1e12,
+            "config": {"workload": "W 4096 x 4096 bf16 N(0, 0.02^2); X 2048 x 4096 bf16 N(0,1) with 0.5 % outlier channels x 50; "
+                                   "16 x 2048 calibration tokens; MXFP4, group 32, round-to-nearest sweep, WUSH transforms"},
+            "cpu_baseline": {"value": (cpu_sweep * hidden / 64 + cpu_fwd * hidden / 64) * 1e3, "unit": "ms (extrapolated to all 4096 "
+                             "output features)", "cores": os.cpu_count() or 1, "kind": "port",
+                             "sample": f"64 of 4096 weight rows: sweep {cpu_sweep:.2f} s, activation quantizer + product "
+                                       f"{cpu_fwd:.2f} s (NumPy float64)"},
+            "gpu_launches": 3 * (16 + 6) + 22, "parity": par, "clocks": clocks.summary()}
+
+
 BLOCK_TOKENS, BLOCK_SEQ = 16 * 2048, 2048
 
 
@@ -735,7 +809,8 @@ def _compact(sec: dict) -> dict:
     """The figures of a section a reader of the one-line record needs."""
     out = {k: sec[k] for k in ("metric", "value", "unit", "ms_per_step", "combine_path", "fused_ms", "nccl_ms",
                                "rtn_ms_per_layer", "gptq_ms_per_layer", "frac", "linear_TFLOPS",
-                               "frac_of_nominal_dense_fp4_per_gpu", "model_forward_ms_80_blocks") if k in sec}
+                               "frac_of_nominal_dense_fp4_per_gpu", "model_forward_ms_80_blocks", "hessian_ms", "sweep_ms",
+                               "forward_ms") if k in sec}
     if "roofline" in sec:
         out["frac"] = sec["roofline"]["frac"]
         out["peak_kind"] = sec["roofline"]["peak_kind"]
@@ -786,6 +861,7 @@ def run_ours(args) -> None:
               "decode": lambda: bench_decode(args, dev, torch, ops, peaks, peak_kind),
               "sharded": lambda: bench_sharded_gemm(args, dev, torch, dist, world, barrier),
               "sweep": lambda: bench_sweep(args, dev, torch),
+              "layer": lambda: bench_layer_4096(args, dev, torch),
               "block": lambda: bench_block(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind),
               "hessian": lambda: bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind,
                                                HESS_HIDDEN=args.hess_hidden)}
@@ -887,6 +963,7 @@ def run_ours(args) -> None:
             extra["gemm_nvfp4"] = single["gemm_nv"]()
             extra["decode"] = single["decode"]()
             extra["sweep"] = single["sweep"]()
+            extra["layer_4096"] = single["layer"]()
         else:
             extra["sharded"] = single["sharded"]()
         extra["block_70b"] = single["block"]()
@@ -989,7 +1066,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="channels of the quantize workload")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time only the kernel launches (no end-to-end or CPU leg); used for profiler captures")
-    ap.add_argument("--only", default="all", choices=["all", "quant", "quant_nv", "gemm", "gemm_nv", "decode", "hessian", "sweep", "sharded", "block"],
+    ap.add_argument("--only", default="all", choices=["all", "quant", "quant_nv", "gemm", "gemm_nv", "decode", "hessian", "sweep", "sharded", "block", "layer"],
                     help="run one section only (profiler captures of a single kernel on a small case)")
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)

@@ -249,7 +249,7 @@ WUSH_API int wush_hessian_finalize_count(float* h, int64_t hidden, const int64_t
  *           or NULL.  Given: the sums are formed by multimem.ld_reduce inside the switch and delivered by
  *           multimem.st; NULL: plain peer loads and stores
  *   counts  DEVICE array of `world` pointers to each rank's int64 local token count (peer-addressable)
- * The 32 x 32 sub-tiles of the range are dealt round-robin to the ranks.  On return (stream order) every
+ * The range is cut into sub-tiles of 8 rows x 128 columns that are dealt round-robin to the ranks.  On return (stream order) every
  * rank's buffer holds, for the sub-tiles this rank owns, the sum over ranks divided by the total token count
  * (lower triangle only; wush_hessian_mirror_tiles rebuilds the rest locally).  Once EVERY rank has run it, all
  * buffers hold the same bits for the range.  The launches must be separated from the producers and consumers of

@@ -188,7 +188,7 @@ def test_tile_panels_and_token_segments():
         p = tile_panels(n_tiles, per_wave)
         assert (p[0][0] == 0 and p[-1][1] == n_tiles) if n_tiles else p == []
         assert all(a[1] == b[0] for a, b in zip(p, p[1:])) and all(b > a for a, b in p)
-        assert all(a % per_wave == 0 for a, _ in p) and len(p) <= 5
+        assert all(a % per_wave == 0 for a, _ in p) and len(p) <= 7
         if n_tiles > per_wave:
             assert p[-1][1] - p[-1][0] <= per_wave              # only the last wave's combine is not hidden
     for tokens in (1, 32768, 49151, 49152, 65536, 262144, 70000):

@@ -2,7 +2,8 @@
 //
 // Every rank holds its raw lower-triangle sum in a buffer that all ranks can address (symmetric memory, one
 // process per GPU).  The kernel takes a range of the 256 x 256 tile list the accumulation kernel walks
-// (hess_tiles.cuh), cut into 32 x 32 sub-tiles that are dealt round-robin to the ranks.  For each sub-tile it
+// (hess_tiles.cuh), cut into sub-tiles of 8 rows x 128 columns (a warp moves one 512-byte row segment per access:
+// long contiguous bursts are what the NVLink packets carry best) that are dealt round-robin to the ranks.  For each sub-tile it
 // owns, a rank sums the sub-tile over all ranks, scales by 1 / total tokens and delivers the result to the
 // same place of every rank's buffer.  A sub-tile is summed by its owner alone, so all ranks end up with
 // bit-identical results, and a given sub-tile of any buffer is only ever touched by its owner's kernel, so
@@ -104,15 +105,15 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const Params p) {
   long long total = 0;
   for (int r = 0; r < p.world; ++r) total += s_counts[r];
   const float scale = 1.0f / (float)(total > 0 ? total : 1);
-  const int row_in = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;   // this thread's float4 inside a sub-tile
+  const int row_in = threadIdx.x >> 5, c4 = (threadIdx.x & 31) * 4;   // this thread's float4 inside an 8 x 128 sub-tile
 
   for (int64_t k = blockIdx.x; k < p.n_items; k += gridDim.x) {
     int bi, bj;
     hess::pair_tile_coords(p.tile_begin + k / p.per_tile, 0, p.nblk, bi, bj);
-    const int sub = p.rank + (int)(k % p.per_tile) * p.world;          // sub-tile (sub / 8, sub % 8) of the tile
-    const int64_t si = (int64_t)bi * 8 + (sub >> 3), sj = (int64_t)bj * 8 + (sub & 7);
-    if (sj > si) continue;                                             // above the diagonal: nothing there
-    const int64_t i = si * 32 + row_in, j = sj * 32 + c4;
+    const int sub = p.rank + (int)(k % p.per_tile) * p.world;          // sub-tile (sub / 2, sub % 2): 32 row groups x 2 halves
+    const int64_t row0 = (int64_t)bi * 256 + (sub >> 1) * 8, col0 = (int64_t)bj * 256 + (sub & 1) * 128;
+    if (col0 > row0 + 7) continue;                                     // entirely above the diagonal: nothing there
+    const int64_t i = row0 + row_in, j = col0 + c4;
     if (i >= p.hidden || j >= p.hidden) continue;                      // hidden % 4 == 0: a float4 never straddles the edge
     const int64_t off = i * p.hidden + j;
     float4 acc;

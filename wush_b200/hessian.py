@@ -103,15 +103,15 @@ def token_segments(tokens: int) -> list[tuple[int, int]]:
     return out
 
 
-def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 5, ratio: float = 3.0) -> list[tuple[int, int]]:
+def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 7, ratio: float = 2.0) -> list[tuple[int, int]]:
     """Cut the tile list [0, n_tiles) into launches whose cross-GPU combine can overlap the next launch.
 
     A launch works on `per_wave` tiles side by side, so a launch over a multiple of per_wave tiles wastes
     nothing.  The last panel is the (possibly partly filled) last wave: its combine is the only one nothing
     hides, so it is kept as small as the tile count allows.  The combine of a panel runs while the NEXT panel is
-    multiplied and costs a fraction of the panel's own multiply time per tile, so the panels before the last shrink
-    geometrically towards the end (each about `ratio` times the next, whole waves): one wave before the last, then
-    about three, nine, ... and the first panel takes what is left."""
+    multiplied and costs (measured, co-resident with the multiply kernel) a bit under half of the panel's own
+    multiply time, so the panels before the last shrink geometrically towards the end (each `ratio` times the
+    next, whole waves): one wave before the last, then two, four, ... and the first panel takes what is left."""
     per_wave = max(1, per_wave)
     waves = -(-n_tiles // per_wave)
     if waves <= 1 or max_panels <= 1:
@@ -240,7 +240,7 @@ class DistributedHessian:
     (gloo) with a stand-in for the CUDA kernels; the defaults call the kernels and need a GPU.
     """
 
-    def __init__(self, hidden: int, device, group=None, panels: int = 5, accumulate_fn=None, finalize_fn=None,
+    def __init__(self, hidden: int, device, group=None, panels: int = 7, accumulate_fn=None, finalize_fn=None,
                  peer: bool | None = None, stage_tokens: int | None = None):
         import os
         import torch.distributed as dist
