@@ -543,6 +543,20 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
     del blk
     events: list = []
     info = {}
+    marks: list = []
+    if args.timeline and world > 1:
+        # CUDA events around every cross-GPU combine (barrier, reduce, barrier, mirror) on the stream it runs on
+        from wush_b200 import hessian as hz
+        inner = hz._PeerBuffers.combine
+
+        def combine(self, hidden, a, b, channel):
+            st = torch.cuda.current_stream(self.flat.device)
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record(st)
+            inner(self, hidden, a, b, channel)
+            ev[1].record(st)
+            marks.append((channel, a, b, ev))
+        hz._PeerBuffers.combine = combine
 
     def job():
         dh = DistributedHessian(HESS_HIDDEN, dev)
@@ -559,6 +573,7 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
         job()
     barrier()
     del events[:]
+    del marks[:]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(dev.index) as clocks:
         e0.record()
@@ -567,6 +582,13 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
         e1.record()
         barrier()
     ms = e0.elapsed_time(e1) / steps
+    timeline = None
+    if marks:
+        per_job = len(marks) // steps
+        last = marks[-per_job:]
+        timeline = {"combines_of_the_last_job": [{"stream": "side (overlaps the next panel's accumulation)" if ch == 0 else "main (tail)",
+                                                   "tiles": [a, b], "us": ev[0].elapsed_time(ev[1]) * 1e3} for ch, a, b, ev in last],
+                    "accumulate_end_to_tail_combine_start_us": events[-1][1].elapsed_time(last[-1][3][0]) * 1e3}
     # the accumulation launches of the timed jobs themselves (events around them on the launching stream)
     kms = sum(a.elapsed_time(b) for a, b in events) / max(1, len(events))
     t = torch.tensor([ms, kms], dtype=torch.float64, device=dev)
@@ -612,7 +634,7 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
             "scaling": "strong", "steps": steps,
             "config": {"workload": f"H = X^T X / N over {HESS_TOKENS} tokens (128 x 2048), hidden {HESS_HIDDEN}, bf16 "
                                    f"in / fp32 out, {local} tokens per GPU; ranks combined by: {info.get('path')}"},
-            "combine_path": info.get("path"),
+            "combine_path": info.get("path"), "timeline": timeline,
             "gpu_launches": steps * launches_per_job,
             "roofline": {"bound": "tensor", "kernel": "hessian_pair_kernel", "achieved": ach, "peak": peak,
                          "unit": "TFLOP/s", "frac": ach / peak,
@@ -1071,6 +1093,8 @@ def main() -> None:
     ap.add_argument("--gemm-size", type=int, default=GEMM_M, help="M = N = K of the GEMM section")
     ap.add_argument("--hess-tokens", type=int, default=HESS_TOKENS)
     ap.add_argument("--hess-hidden", type=int, default=HESS_HIDDEN)
+    ap.add_argument("--timeline", action="store_true",
+                    help="Hessian section on several GPUs: also report CUDA-event durations of every cross-GPU combine")
     args = ap.parse_args()
     g = globals()
     g["TOKENS"], g["HIDDEN"] = args.tokens, args.hidden
