@@ -93,6 +93,21 @@ WUSH_API int wush_fused_quantize_mx(const void* x, const void* mat, int64_t mat_
                            void* stream);
 
 /*
+ * The same kernel with the "quest" scale (MXFP4 only): replaces qutlass.fusedQuantizeMx(method="quest",
+ * return_mask) as bound at inference_lib/src/fp_quant/module/qutlass_ops.py:37-52; the arithmetic is that of the
+ * reference's Triton kernel, inference_lib/src/fp_quant/module/triton/mxfp4.py:64-124.
+ *
+ *   scale = 2^floor(log2(c * std + 1e-8)), std = sqrt(E[y^2] - E[y]^2) over the group's 32 values in fp32,
+ *   c = 2.92247856 / 6;  code = RNE_e2m1(y / scale) saturated at +-6 (no factor 3: the layer's global scales are 1).
+ *   clip_mask  null, or u8 [rows, cols/8]: bit i of byte b is set when element 8b + i was not clipped
+ *              (|y / scale| < 6), the packing the reference's _unpack_mask (linear_fns.py:78-88) reads.
+ * Other arguments as for wush_fused_quantize_mx.
+ */
+WUSH_API int wush_fused_quantize_mx_quest(const void* x, const void* mat, int64_t mat_cols, uint8_t* q, uint8_t* sf,
+                                 int64_t sf_cols, int sf_layout, uint8_t* clip_mask, int64_t rows, int64_t cols,
+                                 int flags, void* stream);
+
+/*
  * Fused per-group transform + NVFP4 quantization (groups of 16, E4M3 scales, fp32 tensor scale).
  *
  * Replaces qutlass.fusedQuantizeNv as bound at

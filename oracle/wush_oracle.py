@@ -339,6 +339,42 @@ def fused_transform_quant(x: np.ndarray, mat: np.ndarray, fmt: str, round_bf16: 
     return out
 
 
+#: Gaussian-optimal scale of the "quest" method (inference_lib/src/fp_quant/module/pseudoquant_linear_fns.py:21)
+QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0
+
+
+def quest_mxfp4(y: np.ndarray, gaussian_scale: float = QUEST_GAUSSIAN_SCALE) -> dict:
+    """MXFP4 with the "quest" scale: the group's standard deviation, not its absolute maximum, sets the shared
+    exponent, and values beyond +-6 clip.  Follows the quest branch of the reference's Triton kernel
+    (inference_lib/src/fp_quant/module/triton/mxfp4.py:64-74 for the scale, :77-118 for the value ladder,
+    :119-124 for the clip mask) in its float32 arithmetic, one operation at a time.
+
+    y: transformed values [..., C], C a multiple of 32.  Returns 'fake_quant' (dequantized float32), 'scaled'
+    (y / 2^e, float32), 'scale_quant' (E8M0 byte: biased exponent e + 127), 'e2m1' (codes, ties toward zero
+    as the ladder's strict comparisons give; 0 quantizes to -0) and 'clip_mask' (|scaled| < 6).
+    """
+    shape = np.shape(y)
+    g = np.asarray(y, dtype=np.float32).reshape(-1, 32)
+    f32 = np.float32
+    mean_sq = (g * g).sum(axis=-1, keepdims=True, dtype=f32) / f32(32)
+    mean = g.sum(axis=-1, keepdims=True, dtype=f32) / f32(32)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        std = np.sqrt(mean_sq - mean * mean)
+        scales = f32(gaussian_scale) * std + f32(1e-8)
+        exps = np.floor(np.log2(scales))
+        shared = np.exp2(exps).astype(f32)
+        scaled = (g / shared).astype(f32)
+    a = np.abs(scaled)
+    idx = ((a > 0.25).astype(np.uint8) + (a > 0.75) + (a > 1.25) + (a > 1.75) + (a > 2.5) + (a > 3.5) + (a > 5)).astype(np.uint8)
+    neg = ~(scaled > 0)
+    codes = (idx | (neg.astype(np.uint8) << 3)).astype(np.uint8)
+    fake = (E2M1_VALUES[codes].astype(f32) * shared).astype(f32)
+    with np.errstate(invalid="ignore"):
+        byte = np.where(np.isfinite(exps), np.clip(exps + 127, 0, 254), 255).astype(np.uint8)
+    return dict(fake_quant=fake.reshape(shape), scaled=scaled.reshape(shape), e2m1=pack_e2m1(codes.reshape(shape)),
+                scale_quant=byte.reshape(shape[:-1] + (shape[-1] // 32,)), clip_mask=(a < 6).reshape(shape))
+
+
 # ----------------------------------------------------------------------------------
 # scale-factor layout consumed by the block-scaled MMA
 # ----------------------------------------------------------------------------------

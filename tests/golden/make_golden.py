@@ -4,6 +4,7 @@ Usage (needs the reference checkout; writes next to this file):
 
     python tests/golden/make_golden.py /path/to/WUSH          # reference_vectors.npz
     python tests/golden/make_golden.py /path/to/WUSH sweep    # sweep_vectors.npz (column sweep)
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/WUSH quest   # quest_vectors.npz
 
 The reference has no numeric tests or fixtures of its own, so these files -- outputs of
 its pure-torch quantizer (src/quantization/wush_gptq.py) on small seeded inputs and
@@ -195,11 +196,61 @@ def sweep_vectors(root: str) -> None:
     print("wrote", os.path.join(HERE, "sweep_vectors.npz"), {k: v.shape for k, v in out.items()})
 
 
+def quest_vectors(root: str) -> None:
+    """The reference's Triton pseudo-quantization kernel (inference_lib/src/fp_quant/module/triton/mxfp4.py) run on
+    CPU by the Triton interpreter (TRITON_INTERPRET=1 must be set before this script starts), quest=True with the
+    constant of pseudoquant_linear_fns.py:21 and, as a cross-check of the other branch, quest=False with 3/4.
+    Inputs are float32 tensors holding bf16-representable values; transforms: identity and normalized Hadamard 32."""
+    import importlib.util
+    if os.environ.get("TRITON_INTERPRET") != "1":
+        sys.exit("set TRITON_INTERPRET=1: the kernel has to run on CPU")
+    spec = importlib.util.spec_from_file_location(
+        "ref_triton_mxfp4", os.path.join(root, "inference_lib/src/fp_quant/module/triton/mxfp4.py"))
+    mx = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mx)
+    kernel = mx.mxfp4_forward_kernel.fn          # the function under the autotuner
+
+    def run(x: torch.Tensor, had: torch.Tensor, quest: bool, gaussian_scale: float):
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        clip = torch.empty(x.shape, dtype=torch.bool)
+        n = x.numel()
+        kernel[((n + 1023) // 1024,)](x_ptr=x, hadamard_matrix_ptr=had.contiguous(), output_ptr=out, clip_mask_ptr=clip,
+                                      n_elements=n, hadamard_dim=32, group_size=32, gaussian_scale=gaussian_scale,
+                                      quest=quest, WRITE_CLIP=True, BLOCK_SIZE=1024)
+        return out.numpy().copy(), clip.numpy().copy()
+
+    g = torch.Generator().manual_seed(777)
+    bf = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    x = torch.randn(64, 128, generator=g)
+    x[:, 7] *= 40.0                                   # an outlier channel: clipped under quest
+    x[3] *= 1e-3
+    x[5] *= 300.0
+    x[8, :32] = 0.0                                   # an all-zero group
+    x[9, :32] = 1.5                                   # a constant group: variance 0 up to rounding
+    x[10, :32] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 4) * torch.tensor([1.0, -1.0] * 16)
+    x = bf(x)
+    h = torch.tensor([[1.0]])
+    while h.shape[0] < 32:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    had = bf(h / 32 ** 0.5)
+    out = {"x": x.numpy(), "hadamard": had.numpy()}
+    for name, mat in (("identity", torch.eye(32)), ("hadamard", had)):
+        for quest, gsc in ((True, 2.92247856 / 6.0), (False, 3.0 / 4.0)):
+            o, c = run(x, mat, quest, gsc)
+            tag = f"{name}_{'quest' if quest else 'absmax'}"
+            out[tag + "_out"], out[tag + "_clip"] = o, c
+    np.savez_compressed(os.path.join(HERE, "quest_vectors.npz"), **out)
+    print("wrote", os.path.join(HERE, "quest_vectors.npz"), {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("WUSH_REFERENCE_ROOT")
     if not root:
-        sys.exit("usage: make_golden.py <reference checkout> [sweep]   (or set WUSH_REFERENCE_ROOT)")
+        sys.exit("usage: make_golden.py <reference checkout> [sweep|quest]   (or set WUSH_REFERENCE_ROOT)")
     if len(sys.argv) > 2 and sys.argv[2] == "sweep":
         sweep_vectors(root)
+    elif len(sys.argv) > 2 and sys.argv[2] == "quest":
+        quest_vectors(root)
     else:
         main(root)

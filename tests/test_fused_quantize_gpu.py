@@ -143,8 +143,14 @@ def test_public_ops_shapes_and_errors():
     assert sf3.shape == (256, 260) and sf3.dtype == torch.float8_e4m3fn
     with pytest.raises(Exception):
         ops.fused_quantize_mx_op(x.cpu(), h.cpu(), "abs_max", False)       # no CPU fallback
-    with pytest.raises(NotImplementedError):
-        ops.fused_quantize_mx_op(x, h, "quest", False)
+    with pytest.raises(ValueError):
+        ops.fused_quantize_mx_op(x, h, "median", False)
+    q4, sf4, mask4 = ops.fused_quantize_mx_op(x, h, "quest", True)
+    assert q4.shape == q2.shape and sf4.shape == sf2.shape and mask4.shape == mask2.shape
+    assert ops.fused_quantize_mx_op(x, h, "quest", False)[2] is None
+    # the per-group op has no method of its own: whatever is passed, it scales by the absolute maximum
+    q5, sf5, _ = ops.fused_quantize_mx_wush_op(x, wm, "quest", False)
+    assert torch.equal(q5, q) and torch.equal(sf5.view(torch.uint8), sf.view(torch.uint8))
     empty = ops.fused_quantize_mx_op(x[:0], h, "abs_max", False)
     assert empty[0].shape == (0, (4096 + 64) // 2)
 
@@ -277,3 +283,80 @@ def test_swiglu_pass_matches_torch():
     ulp = want.float().abs() * 2.0 ** -7                        # one bf16 step at the value's magnitude, at most
     assert bool((diff <= ulp + 1e-30).all())
     assert float((diff > 0).float().mean()) <= 5e-3             # hardware exponential: a rare last-bit difference
+
+
+# ---- "quest" scaling ---------------------------------------------------------------------------------------------
+
+_TIES = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+
+
+def _quest_check(x_bf16, mat_np, blocked=False):
+    """Kernel (codes, scale bytes, packed clip mask) against the oracle's quest restatement applied to the float32
+    transform.  Scale bytes: equal except where the fp32 sums, taken in another order, straddle a power of two
+    (budget 1e-3 of the groups).  In groups with equal scales: clip flags equal, codes equal except on exact
+    rounding boundaries, where the kernel rounds to the even code and the reference's ladder toward zero."""
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    rows, cols = x_bf16.shape
+    mask = torch.zeros(rows, cols // 8, dtype=torch.uint8, device=dev)
+    q, sf = ops._quantize(x_bf16.to(dev), synth.to_bf16_tensor(mat_np).to(dev), "mx", None,
+                          sf_layout=1 if blocked else 0, quest=True, clip_mask=mask)
+    torch.cuda.synchronize()
+    q, sf, mask = np_u8(q), np_u8(sf), np_u8(mask)
+    x64 = synth.bf16_to_f64(x_bf16)
+    t = np.asarray(mat_np, dtype=np.float64)
+    y = wo.block_transform(x64, wo.matrix_to_transform(t) if t.shape[1] != 32 else t.T).astype(np.float32)
+    ref = wo.quest_mxfp4(y)
+    want_sf = ref["scale_quant"]
+    if blocked:
+        assert mismatch_fraction(sf.reshape(-1), wo.to_blocked(want_sf).reshape(-1)) < 1e-3
+        return
+    sf_valid = sf[:rows, : cols // 32]
+    same = sf_valid == want_sf
+    assert same.mean() > 1 - 1e-3, same.mean()
+    same_e = np.repeat(same, 32, axis=1)
+    bits = ((mask[:, :, None] >> np.arange(8, dtype=np.uint8)) & 1).reshape(rows, cols).astype(bool)
+    assert np.array_equal(bits[same_e], ref["clip_mask"][same_e])
+    got = canon_codes(q)
+    want = canon_codes(ref["e2m1"])
+    tie = np.isin(np.abs(ref["scaled"]), _TIES)
+    assert np.array_equal(got[same_e & ~tie], want[same_e & ~tie])
+    # on a tie either neighbour is a nearest value: same distance from the scaled value
+    vg, vw = wo.E2M1_VALUES[got], wo.E2M1_VALUES[want]
+    sc = ref["scaled"].astype(np.float64)
+    assert np.array_equal(np.abs(vg - sc)[same_e & tie], np.abs(vw - sc)[same_e & tie])
+    assert 0.5 < ref["clip_mask"].mean() <= 1.0
+
+
+@pytest.mark.parametrize("kind", ["identity", "hadamard"])
+@pytest.mark.parametrize("rows,cols", [(64, 128), (333, 4096), (1, 32), (130, 4096 + 64)])
+def test_quest_matches_oracle(kind, rows, cols):
+    x = synth.activations(rows, cols, seed=rows + cols)
+    _quest_check(x, _matrix(kind, "mx", cols))
+
+
+def test_quest_blocked_scales():
+    _quest_check(synth.activations(300, 1024, seed=4), _matrix("hadamard", "mx", 1024), blocked=True)
+
+
+def test_quest_against_triton_golden():
+    """The inputs of the committed vectors (outputs of the reference's Triton kernel) through the kernel and through
+    the pseudo-quantization wrapper that mirrors the reference's."""
+    import os
+    from wush_b200 import pseudo_quant
+    d = np.load(os.path.join(os.path.dirname(__file__), "golden", "quest_vectors.npz"))
+    x = torch.from_numpy(d["x"]).to(torch.bfloat16)
+    _quest_check(x, np.eye(32))
+    _quest_check(x, d["hadamard"].astype(np.float64))
+    dev = torch.device("cuda:0")
+    for name, mat in (("identity", torch.eye(32)), ("hadamard", torch.from_numpy(d["hadamard"]))):
+        out, clip = pseudo_quant.mxfp4_forward_kernel_wrapper(x.to(dev), mat.to(dev, torch.bfloat16), return_clip_mask=True,
+                                                              quest=True, gaussian_scale=2.92247856 / 6.0)
+        want = torch.from_numpy(d[f"{name}_quest_out"]).to(torch.bfloat16).float().numpy()
+        got = out.float().cpu().numpy()
+        assert out.dtype == torch.bfloat16 and out.shape == x.shape
+        # identical except on rounding ties and where a group's scale moved (sum order): well under 2 % here
+        assert np.mean(got != want) < 0.02, np.mean(got != want)
+        assert np.mean(clip.cpu().numpy() != d[f"{name}_quest_clip"]) < 1e-3
+    with pytest.raises(NotImplementedError):
+        pseudo_quant.mxfp4_forward_kernel_wrapper(x.to(dev), torch.eye(32, device=dev), quest=True)   # 3/4 with quest

@@ -71,8 +71,34 @@ def test_hadamard_linear_quantizes_its_own_weight():
     y = layer(x.to(dev)).double().cpu().numpy()
     exact = synth.bf16_to_f64(x) @ synth.bf16_to_f64(w).T
     assert np.linalg.norm(y - exact) / np.linalg.norm(exact) < 0.25
-    with pytest.raises(NotImplementedError):
-        FPQuantConfig(forward_method="quest") and FPQuantLinear(512, 256, FPQuantConfig(forward_method="quest"), device=dev)
+    with pytest.raises(NotImplementedError):       # the per-group transform has no quest variant (nor in the reference)
+        FPQuantLinear(512, 256, FPQuantConfig(forward_method="quest", transform_init="wush"), device=dev)
+    with pytest.raises(ValueError):
+        FPQuantLinear(512, 256, FPQuantConfig(forward_method="median"), device=dev)
+
+
+def test_quest_linear():
+    """forward_method="quest": global scales 1.0, weights and activations scaled by their groups' standard deviation
+    (with clipping); the layer output is the dequantized product of the two quantized operands."""
+    from oracle import wush_oracle as wo
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    layer = FPQuantLinear(512, 256, FPQuantConfig(forward_method="quest"), bias=False, device=dev)
+    assert float(layer.weight_global_scale) == 1.0 and float(layer.act_global_scale) == 1.0
+    w = synth.weights(256, 512, seed=16)
+    layer.weight.data.copy_(w.to(dev))
+    layer.pre_forward()
+    x = synth.activations(96, 512, seed=17)
+    y = layer(x.to(dev)).double().cpu().numpy()
+    had = synth.bf16_to_f64(layer.forward_hadamard_matrix.cpu())
+    deq = lambda t: wo.quest_mxfp4(wo.block_transform(synth.bf16_to_f64(t), had.T).astype(np.float32))["fake_quant"].astype(np.float64)
+    want = deq(x) @ deq(w).T
+    assert np.linalg.norm(y - want) <= 2e-2 * np.linalg.norm(want)          # ties and bf16 output rounding
+    exact = synth.bf16_to_f64(x) @ synth.bf16_to_f64(w).T
+    assert np.linalg.norm(y - exact) / np.linalg.norm(exact) < 0.3
+    nv = FPQuantLinear(512, 256, FPQuantConfig(forward_dtype=FPQuantDtype.NVFP4, forward_method="quest", hadamard_group_size=16),
+                       bias=False, device=dev)
+    assert float(nv.weight_global_scale) == 10.0
 
 
 @pytest.mark.parametrize("fmt,rtn", [("mxfp4", False), ("nvfp4", True)])

@@ -56,6 +56,7 @@ def load() -> ctypes.CDLL:
     sigs = {
         "wush_b200_arch": [],
         "wush_fused_quantize_mx": [vp, vp, i64, vp, vp, i64, i32, i64, i64, i32, vp],
+        "wush_fused_quantize_mx_quest": [vp, vp, i64, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_fused_quantize_nv": [vp, vp, i64, vp, vp, vp, i64, i32, i64, i64, i32, vp],
         "wush_fused_quantize_debug": [i32, vp, vp, i64, vp, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_fused_quantize_strided": [i32, vp, i64, vp, i64, vp, vp, i64, vp, i64, i32, i64, vp, vp, i64, i64, i32, vp],

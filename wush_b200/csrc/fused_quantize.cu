@@ -58,6 +58,7 @@ struct QuantParams {
   // of the separate bf16 steps
   const float* row_scale;           // fp32 [rows] or null
   const __nv_bfloat16* col_scale;   // bf16 [cols] or null (both or none)
+  uint8_t* clip_mask;               // quest only, optional: [rows, cols / 8], bit i of byte b = element 8b + i not clipped
 };
 
 __device__ __forceinline__ void mma_bf16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -163,6 +164,40 @@ __device__ __forceinline__ void quantize_row(float (&v)[8], float gs, float gs6,
   if (!NV && amax == 0.0f) packed = 0x88888888u;  // the reference encodes an all-zero group as -0
 }
 
+// "quest" scaling of one MXFP4 group (the 4 lanes of the row hold its 32 values): the shared exponent comes from
+// the group's standard deviation, 2^floor(log2(c * std + 1e-8)) with c = 2.92247856 / 6, and values beyond +-6
+// saturate.  Each fp32 operation is rounded on its own, in the order of the reference's Triton kernel
+// (inference_lib/src/fp_quant/module/triton/mxfp4.py:64-74); only the order of the two 32-term sums differs.
+// keep: bit i set when |v[i] / 2^e| < 6 (the reference's clip mask, ibid. :119-124).
+constexpr float kQuestScale = (float)(2.92247856 / 6.0);
+__device__ __forceinline__ void quantize_row_quest(float (&v)[8], uint32_t& packed, uint32_t& scale_byte,
+                                                   uint32_t& keep) {
+  float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    s1 = __fadd_rn(s1, v[i]);
+    s2 = __fadd_rn(s2, __fmul_rn(v[i], v[i]));
+  }
+  s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, 1));
+  s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 1));
+  s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, 2));
+  s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 2));
+  const float mean = __fmul_rn(s1, 0.03125f), mean_sq = __fmul_rn(s2, 0.03125f);
+  const float sd = __fsqrt_rn(__fsub_rn(mean_sq, __fmul_rn(mean, mean)));
+  const float scale = __fadd_rn(__fmul_rn(kQuestScale, sd), 1e-8f);   // >= 1e-8: a normal number, or NaN / inf
+  const uint32_t e = (__float_as_uint(scale) >> 23) & 0xFFu;          // biased floor(log2(scale)); 255 for NaN / inf
+  scale_byte = e;
+  // 2^(127 - e), exact for e <= 253; a NaN / inf scale poisons the group as the reference's division does
+  const float mul = e >= 254u ? __uint_as_float(0x7fc00000u) : __uint_as_float((254u - e) << 23);
+  keep = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] *= mul;
+    keep |= (fabsf(v[i]) < 6.0f ? 1u : 0u) << i;
+  }
+  packed = pack_e2m1x8(v);
+}
+
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
 }
@@ -203,7 +238,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 
 // RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
 // the transformed values.  PRO: scale the activations by row_scale / col_scale first (see QuantParams).
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false>
+// QUEST (MXFP4 only): standard-deviation scale with clipping instead of the absolute-maximum scale.
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false>
 __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
   constexpr int TD = NV ? 16 : 32;       // transform size == quantization group
   constexpr int GPC = kChunk / TD;       // scale groups per chunk
@@ -433,7 +469,14 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
             *reinterpret_cast<float4*>(t4 + 4) = make_float4(v[4], v[5], v[6], v[7]);
           }
           uint32_t packed, sbyte;
-          quantize_row<NV>(v, gs, gs6, packed, sbyte);
+          if (QUEST) {
+            uint32_t keep;
+            quantize_row_quest(v, packed, sbyte, keep);
+            if (p.clip_mask != nullptr && r0 + trow < row_end)
+              p.clip_mask[(int64_t)(r0 + trow) * (p.cols >> 3) + ((col0 + 8 * q4) >> 3)] = (uint8_t)keep;
+          } else {
+            quantize_row<NV>(v, gs, gs6, packed, sbyte);
+          }
           *reinterpret_cast<uint32_t*>(out_q + out_q_lane + (trow - g) * kOutRow) = packed;
           if (sf_writer) out_sf[out_sf_lane + (trow - g) * kSfRow] = (uint8_t)sbyte;
         }
@@ -478,7 +521,7 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
 // Grid: x = slabs, y = row splits.  Every CTA takes an equal share (+-1) of the 32-row tiles.
 // The number of row splits is the largest that keeps all CTAs co-resident in `waves` waves of
 // (SMs x CTAs per SM), so the last wave is not a mostly empty tail.
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false>
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
   const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
@@ -494,7 +537,7 @@ static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   if (splits > 65535) splits = 65535;
   p.row_splits = (int)splits;
   dim3 grid((unsigned)slabs, (unsigned)splits);
-  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO>;
+  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO, QUEST>;
   constexpr int smem = kQuantSmem;
   static PerDevice attr_set;     // per instantiation and device
   const int rc = opt_in_smem(attr_set, kern, smem);
@@ -544,6 +587,24 @@ extern "C" int wush_fused_quantize_mx(const void* x, const void* mat, int64_t ma
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
                 sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
   return launch_quant<false, false>(p, (cudaStream_t)stream);
+}
+
+extern "C" int wush_fused_quantize_mx_quest(const void* x, const void* mat, int64_t mat_cols, uint8_t* q, uint8_t* sf,
+                                            int64_t sf_cols, int sf_layout, uint8_t* clip_mask, int64_t rows,
+                                            int64_t cols, int flags, void* stream) {
+  int rc = check_quant_args(false, x, mat, mat_cols, nullptr, q, sf, sf_cols, sf_layout, rows, cols, flags);
+  if (rc != WUSH_OK) return rc;
+  if (rows == 0) return WUSH_OK;
+  if (const int rc100 = require_sm100()) return rc100;
+  QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
+                sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr,
+                clip_mask};
+  const bool bl = sf_layout == WUSH_SF_BLOCKED;
+  if (p.round_bf16)
+    return bl ? launch_quant_t<false, false, true, true, false, true>(p, (cudaStream_t)stream)
+              : launch_quant_t<false, false, true, false, false, true>(p, (cudaStream_t)stream);
+  return bl ? launch_quant_t<false, false, false, true, false, true>(p, (cudaStream_t)stream)
+            : launch_quant_t<false, false, false, false, false, true>(p, (cudaStream_t)stream);
 }
 
 extern "C" int wush_fused_quantize_nv(const void* x, const void* mat, int64_t mat_cols, const float* global_scale,

@@ -42,8 +42,12 @@ class FPQuantConfig:
 def validate_config(config: FPQuantConfig) -> None:
     if config.forward_dtype not in (FPQuantDtype.MXFP4, FPQuantDtype.NVFP4):
         raise ValueError(f"Unsupported forward dtype: {config.forward_dtype}")
-    if config.forward_method != "abs_max":
-        raise NotImplementedError("only forward_method='abs_max' is implemented")
+    if config.forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {config.forward_method}")
+    if config.forward_method == "quest" and config.forward_dtype == FPQuantDtype.MXFP4 and config.transform_init == "wush":
+        # the reference's per-group op ignores the method (qutlass_ops.py:110-125) while its layer sets the global
+        # scales for it (linear.py:207-211): the two do not fit together there either
+        raise NotImplementedError("forward_method='quest' needs a shared square transform (hadamard or identity)")
     want = 32 if config.forward_dtype == FPQuantDtype.MXFP4 else 16
     if config.hadamard_group_size != want:
         raise NotImplementedError(f"{config.forward_dtype.value} needs hadamard_group_size == {want} here")
@@ -58,12 +62,16 @@ def _fmt(dtype: FPQuantDtype) -> str:
 def forward_quantize(x: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor, dtype: FPQuantDtype,
                      forward_method: str, blocked: bool = False):
     """(codes u8, scales u8) of a 2-D bf16 tensor; reference: linear_fns.py:29-62.  With ``blocked`` the
-    scales come out in the layout the GEMM consumes (no separate re-layout pass)."""
-    if forward_method != "abs_max":
-        raise NotImplementedError("only forward_method='abs_max' is implemented")
+    scales come out in the layout the GEMM consumes (no separate re-layout pass).  As in the reference, the method
+    only matters for MXFP4 with a shared square transform: "quest" scales by the group's standard deviation."""
+    if forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {forward_method}")
     layout = _lib.SF_BLOCKED if blocked else _lib.SF_ROW_MAJOR
     gs = global_scale.float() if dtype == FPQuantDtype.NVFP4 else None
-    return ops._quantize(x.to(torch.bfloat16), hadamard_matrix.to(torch.bfloat16), _fmt(dtype), gs, sf_layout=layout)
+    quest = (forward_method == "quest" and dtype == FPQuantDtype.MXFP4
+             and hadamard_matrix.shape[0] == hadamard_matrix.shape[1])
+    return ops._quantize(x.to(torch.bfloat16), hadamard_matrix.to(torch.bfloat16), _fmt(dtype), gs, sf_layout=layout,
+                         quest=quest)
 
 
 def _hadamard(n: int, device, dtype) -> torch.Tensor:
@@ -90,8 +98,13 @@ class FPQuantLinear(nn.Module):
         # 3.0 whenever the method is abs_max, for both formats, like the reference's pre_forward (linear.py:206-217:
         # its abs_max branch comes before the NVFP4 one); exported WUSH checkpoints carry their own value (10.0 for
         # NVFP4, wush_gptq.py:588) and overwrite it through the state dict.  Buffers in the module dtype, as there.
-        self.register_buffer("weight_global_scale", torch.tensor([3.0], **kw))
-        self.register_buffer("act_global_scale", torch.tensor([3.0], **kw))
+        # MXFP4 with the quest method: 1.0 (its codes carry no implicit factor); NVFP4 with quest: 10.0 (ibid.)
+        if config.forward_method == "quest":
+            gsv = 1.0 if config.forward_dtype == FPQuantDtype.MXFP4 else 10.0
+        else:
+            gsv = 3.0
+        self.register_buffer("weight_global_scale", torch.tensor([gsv], **kw))
+        self.register_buffer("act_global_scale", torch.tensor([gsv], **kw))
         cols = in_features if config.transform_init == "wush" else g
         self.register_buffer("forward_hadamard_matrix", torch.zeros(g, cols, **kw))
         self.register_buffer("backward_hadamard_matrix", torch.zeros(g, cols, **kw))

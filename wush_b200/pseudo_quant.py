@@ -5,8 +5,9 @@
 scales; the values are rebuilt from them.
 
 Differences from the Triton kernels: ties round to the even code (the reference's torch quantizer's rule; the
-Triton kernels round ties toward zero), and only the abs-max scaling the WUSH pipeline uses is implemented
-(``quest=False``, ``gaussian_scale=3/4``).
+Triton kernels round ties toward zero), and the scale constant is not free: ``quest=False`` goes with
+``gaussian_scale=3/4`` (abs-max scaling, what the WUSH pipeline uses) and ``quest=True`` with
+``gaussian_scale=2.92247856/6``, the two pairs the reference's own caller passes (pseudoquant_linear_fns.py:20-26).
 """
 from __future__ import annotations
 
@@ -17,20 +18,45 @@ from . import qutlass_ops as ops
 from .gptq import dequantize
 
 
+QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0
+
+
 def _flat(x: torch.Tensor) -> torch.Tensor:
     return x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
 
 
+def _values_times_scale(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    """E2M1 values times their group's E8M0 scale, exactly (quest codes carry no global factor)."""
+    lut = torch.tensor([0., .5, 1., 1.5, 2., 3., 4., 6., -0., -.5, -1., -1.5, -2., -3., -4., -6.],
+                       dtype=torch.float32, device=q.device)
+    vals = lut[torch.stack([q & 0xF, q >> 4], dim=-1).flatten(-2).long()]
+    scale = sf.contiguous().view(torch.float8_e8m0fnu).to(torch.float32)
+    return (vals.unflatten(-1, (-1, 32)) * scale.unsqueeze(-1)).flatten(-2)
+
+
 def mxfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor, return_clip_mask: bool = False,
                                  gaussian_scale: float = 3 / 4, quest: bool = True):
-    """(dequantized tensor like x, clip mask | None).  x @ hadamard_matrix per 32-element group, E8M0 abs-max
-    scale, E2M1 values.  The abs-max scale never clips, so the mask is all True."""
-    if quest or abs(gaussian_scale - 0.75) > 1e-12:
-        raise NotImplementedError("only quest=False with gaussian_scale=3/4 (abs-max scaling) is implemented")
+    """(dequantized tensor like x, clip mask | None).  x @ hadamard_matrix per 32-element group, E8M0 scale, E2M1
+    values.  quest=False: abs-max scale, which never clips, so the mask is all True.  quest=True: the scale follows
+    the group's standard deviation and the mask marks the values inside +-6 scales."""
     if hadamard_matrix.shape[-1] != 32:
         raise NotImplementedError("the transform must be 32 x 32 (one scale group)")
     xf = _flat(x)
-    q, sf = ops._quantize(xf, hadamard_matrix.to(device=x.device, dtype=torch.bfloat16), "mx", None)
+    mat = hadamard_matrix.to(device=x.device, dtype=torch.bfloat16)
+    if quest:
+        if abs(gaussian_scale - QUEST_GAUSSIAN_SCALE) > 1e-9:
+            raise NotImplementedError("quest=True is implemented for gaussian_scale=2.92247856/6 only")
+        packed = torch.empty(xf.shape[0], xf.shape[1] // 8, dtype=torch.uint8, device=xf.device) if return_clip_mask else None
+        q, sf = ops._quantize(xf, mat, "mx", None, quest=True, clip_mask=packed)
+        out = _values_times_scale(q, sf[: xf.shape[0], : xf.shape[1] // 32]).to(x.dtype).reshape(x.shape)
+        mask = None
+        if return_clip_mask:
+            bits = (packed.unsqueeze(-1) >> torch.arange(8, device=xf.device, dtype=torch.uint8)) & 1
+            mask = bits.reshape(xf.shape).to(torch.bool).reshape(x.shape)
+        return out, mask
+    if abs(gaussian_scale - 0.75) > 1e-12:
+        raise NotImplementedError("quest=False is implemented for gaussian_scale=3/4 (abs-max scaling) only")
+    q, sf = ops._quantize(xf, mat, "mx", None)
     out = dequantize(q, sf[: xf.shape[0], : xf.shape[1] // 32], "mxfp4").to(x.dtype).reshape(x.shape)
     return out, (torch.ones_like(x, dtype=torch.bool) if return_clip_mask else None)
 

@@ -43,8 +43,12 @@ def _alloc_scales(rows: int, groups: int, device) -> torch.Tensor:
 
 
 def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor],
-              sf_layout: int = _lib.SF_ROW_MAJOR, round_bf16: bool = False):
+              sf_layout: int = _lib.SF_ROW_MAJOR, round_bf16: bool = False, quest: bool = False,
+              clip_mask: Optional[torch.Tensor] = None):
+    """quest (MXFP4 only): standard-deviation scale with clipping; clip_mask: u8 [rows, cols/8] the kernel fills."""
     _require_cuda(x_flat, matrix, global_scale)
+    if quest and fmt != "mx":
+        raise ValueError("the quest method exists for MXFP4 only")
     if x_flat.dim() != 2:
         raise ValueError("x_flat must be 2-D (tokens, channels)")
     if x_flat.dtype != torch.bfloat16 or matrix.dtype != torch.bfloat16:
@@ -66,7 +70,12 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
         return q, sf
     flags = _lib.QUANT_ROUND_BF16 if round_bf16 else 0
     with torch.cuda.device(x_flat.device):
-        if fmt == "mx":
+        if quest:
+            rc = lib.wush_fused_quantize_mx_quest(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], q.data_ptr(),
+                                                  sf.data_ptr(), sf.shape[1], sf_layout,
+                                                  clip_mask.data_ptr() if clip_mask is not None else None, rows, cols,
+                                                  flags, _stream(x_flat))
+        elif fmt == "mx":
             rc = lib.wush_fused_quantize_mx(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], q.data_ptr(),
                                             sf.data_ptr(), sf.shape[1], sf_layout, rows, cols, flags, _stream(x_flat))
         else:
@@ -74,7 +83,7 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
             rc = lib.wush_fused_quantize_nv(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], gs.data_ptr(),
                                             q.data_ptr(), sf.data_ptr(), sf.shape[1], sf_layout, rows, cols, flags,
                                             _stream(x_flat))
-    _lib.check(rc, f"wush_fused_quantize_{fmt}")
+    _lib.check(rc, f"wush_fused_quantize_{fmt}{'_quest' if quest else ''}")
     return q, sf
 
 
@@ -160,11 +169,18 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 @torch.library.custom_op("wush_b200::fused_quantize_mx_op", mutates_args=())
 def _fused_quantize_mx(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
-                       return_mask: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    if forward_method != "abs_max":
-        raise NotImplementedError("only forward_method='abs_max' is implemented (the method WUSH checkpoints use)")
-    q, sf = _quantize(x_flat, hadamard_matrix, "mx", None)
-    return q, sf.view(torch.float8_e8m0fnu)
+                       return_mask: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    if forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {forward_method}")
+    rows, cols = x_flat.shape
+    if forward_method == "quest":
+        mask = torch.empty(rows, cols // 8 if return_mask else 0, dtype=torch.uint8, device=x_flat.device)
+        q, sf = _quantize(x_flat, hadamard_matrix, "mx", None, quest=True, clip_mask=mask if return_mask else None)
+    else:
+        # the absolute-maximum scale never clips (|3 y / scale| < 6): every bit of the packed mask is set
+        mask = torch.full((rows, cols // 8 if return_mask else 0), 0xFF, dtype=torch.uint8, device=x_flat.device)
+        q, sf = _quantize(x_flat, hadamard_matrix, "mx", None)
+    return q, sf.view(torch.float8_e8m0fnu), mask
 
 
 @_fused_quantize_mx.register_fake
@@ -172,27 +188,24 @@ def _(x_flat, hadamard_matrix, forward_method, return_mask):
     rows, groups = x_flat.size(0), x_flat.size(1) // 32
     pr, pc = _padded_scale_shape(rows, groups)
     return (torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device),
-            torch.empty(pr, pc, dtype=torch.float8_e8m0fnu, device=x_flat.device))
-
-
-def _all_kept_mask(x_flat: torch.Tensor) -> torch.Tensor:
-    # abs_max scaling never clips (|3x/scale| < 6), so every bit of the packed mask is set
-    return torch.full((x_flat.size(0), x_flat.size(1) // 8), 0xFF, dtype=torch.uint8, device=x_flat.device)
+            torch.empty(pr, pc, dtype=torch.float8_e8m0fnu, device=x_flat.device),
+            torch.empty(rows, groups * 4 if return_mask else 0, dtype=torch.uint8, device=x_flat.device))
 
 
 def fused_quantize_mx_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
                          return_mask: bool):
-    """(e2m1 u8 [T, C/2], e8m0 [ceil(T/128)*128, ceil(C/32/4)*4], mask | None).
-    Reference: qutlass_ops.py:37-72 (shared square transform)."""
-    q, sf = _fused_quantize_mx(x_flat, hadamard_matrix, forward_method, return_mask)
-    return q, sf, (_all_kept_mask(x_flat) if return_mask else None)
+    """(e2m1 u8 [T, C/2], e8m0 [ceil(T/128)*128, ceil(C/32/4)*4], packed clip mask u8 [T, C/8] | None).
+    forward_method "abs_max" or "quest".  Reference: qutlass_ops.py:37-72 (shared square transform)."""
+    q, sf, mask = _fused_quantize_mx(x_flat, hadamard_matrix, forward_method, return_mask)
+    return q, sf, (mask if return_mask else None)
 
 
 def fused_quantize_mx_wush_op(x_flat: torch.Tensor, wush_matrix: torch.Tensor, forward_method: str,
                               return_mask: bool):
-    """Per-group 32x32 transform given as a (32, C) matrix.  Reference: qutlass_ops.py:110-143."""
-    q, sf = _fused_quantize_mx(x_flat, wush_matrix, forward_method, return_mask)
-    return q, sf, (_all_kept_mask(x_flat) if return_mask else None)
+    """Per-group 32x32 transform given as a (32, C) matrix.  Like the reference's op (qutlass_ops.py:110-143, whose
+    kernel takes no method), this one always uses the absolute-maximum scale whatever `forward_method` says."""
+    q, sf, mask = _fused_quantize_mx(x_flat, wush_matrix, "abs_max", return_mask)
+    return q, sf, (mask if return_mask else None)
 
 
 @torch.library.custom_op("wush_b200::fused_quantize_nv_op", mutates_args=())
