@@ -380,13 +380,23 @@ def bench_decode(args, dev, torch, ops, peaks, peak_kind) -> dict:
         wsf = torch.randint(118, 126, (n, k // 32), generator=gen, device=dev, dtype=torch.uint8)
         wsb = ops.to_blocked(wsf).view(-1)
         alpha = torch.tensor([1.0 / 9.0], device=dev)
+        # consecutive calls read different copies of the weights, 256 MB in total (twice the L2), as the layers of
+        # a model would: the small-M numbers are HBM numbers, not L2 numbers
+        copies = [(wq, wsb)] + [(wq.clone(), wsb.clone()) for _ in range(int(np.ceil(2.56e8 / (n * k * 0.53125))) - 1)]
         for m in DECODE_M:
             xq = torch.randint(0, 256, (m, k // 2), generator=gen, device=dev, dtype=torch.uint8)
             xsf = torch.randint(122, 130, (m, k // 32), generator=gen, device=dev, dtype=torch.uint8)
             xsb = ops.to_blocked(xsf).view(-1)
-            fn = lambda: ops.matmul_fp4_blocked(xq, wq, xsb, wsb, alpha, "mx")
+            turn = [0]
+
+            def fn():
+                wq_i, wsb_i = copies[turn[0] % len(copies)] if m <= 128 else copies[0]
+                turn[0] += 1
+                return ops.matmul_fp4_blocked(xq, wq_i, xsb, wsb_i, alpha, "mx")
             for _ in range(3):
-                y = fn()
+                fn()
+            turn[0] = 0
+            y = fn()                       # the parity check below reads the product with the first copy
             steps = 20 if m <= 1024 else 10
             us = _time_steps(fn, steps, torch, graph=True) * 1e3
             wbytes = n * k / 2 + n * k / 32 + m * k / 2 + m * k / 32 + 2.0 * m * n
@@ -402,8 +412,9 @@ def bench_decode(args, dev, torch, ops, peaks, peak_kind) -> dict:
     return {"metric": "mxfp4_decoder_shape_gemm_us", "unit": "us per call (device, graph replay)", "grid": grid,
             "value": grid["N4096_K4096_M1"]["us"],
             "config": {"workload": "MXFP4 GEMM, (N,K) of a hidden-4096 / FFN-14336 decoder layer x M in {1,16,128,1024,8192}, "
-                                   "random codes, E8M0 scales within 2^-9..2^2; one launch per call (split K finished by "
-                                   "the last-arriving warp)"},
+                                   "random codes, E8M0 scales within 2^-9..2^2; one launch per call (M <= 4: matrix-vector "
+                                   "kernel on the CUDA cores; above: tcgen05 GEMM, K split inside a cluster); for M <= 128 "
+                                   "successive calls read different weight copies (256 MB in rotation, twice the L2)"},
             "peak_kind": f"frac_hbm of {peak_kind} copy bandwidth (weights + activations + output once); frac_tensor of 4 x "
                          f"{peak_kind} bf16 burst",
             "gpu_launches": sum(3 + 2 * (20 if m <= 1024 else 10) for _ in DECODE_SHAPES for m in DECODE_M),

@@ -295,8 +295,11 @@ WUSH_API int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const i
  *              hold finite scale bytes (zero is fine)
  *   alpha      device pointer to one fp32 (1 / (weight_global_scale * act_global_scale) in the reference)
  *   y          bf16 [m, n] row-major, 16-byte aligned; n % 8 == 0, k % 128 == 0
- *   splits     0 = choose automatically.  When few output tiles exist (small m: the GEMM then streams the weights
- *              once and is bound by memory) the K range is split over 2, 4 or 8 CTAs that form a thread-block cluster;
+ *   splits     0 = choose automatically.  m <= 4 (decode; WUSH_B200_GEMV_MAX_M lowers the limit, 0 switches it off):
+ *              a matrix-vector kernel streams the weight bytes once with plain loads and multiplies on the CUDA cores
+ *              (exact fp16 sums of 8 products, fp32 from there on), 16 weight rows per CTA, no K splits.
+ *              Otherwise, when few output tiles exist (small m: the GEMM streams the weights once and is bound by
+ *              memory) the K range is split over 2, 4 or 8 CTAs that form a thread-block cluster;
  *              their fp32 partial tiles meet in distributed shared memory and are added in split order, in the same
  *              launch, without scratch memory.
  *              > 0 forces that many K splits the other way: fp32 partial tiles [splits, m, n] in `workspace` and a

@@ -127,3 +127,42 @@ def test_activations_given_as_stacked_k_shards(fmt, m):
         stack_s[s, : sf.numel()] = sf.view(-1)
     got = ops.matmul_fp4_blocked(stack_q, wq, stack_s.view(-1), ws.view(-1), alpha, fmt, rows=m)
     assert torch.equal(got, want)
+
+
+# ---- decode: 1..4 activation rows take the matrix-vector kernel ---------------------------------------------------
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (1, 1000, 4096), (2, 1024, 4096), (3, 40, 1152), (4, 4096, 14336),
+                                   (1, 14336, 4096)])
+def test_matrix_vector_kernel_matches_oracle(fmt, m, n, k):
+    """Every output against the float64 oracle; n not a multiple of the 16 rows of a CTA, k from one 16-byte unit per
+    lane to several passes per warp.  The group sums are exact, so the error is the fp32 order of additions plus the
+    final bf16 rounding."""
+    rel, got, want = _run(fmt, m, n, k, seed=m + n)
+    assert rel <= 3e-3, rel
+    assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("fmt", ["mx", "nv"])
+def test_matrix_vector_kernel_agrees_with_the_tensor_core_path(fmt):
+    """Same operands through the matrix-vector kernel (automatic for m <= 4) and through the tcgen05 GEMM (forced by
+    asking for one K split): equal up to the order of fp32 additions -- at most one bf16 ulp -- with bias and
+    residual applied the same way."""
+    from wush_b200 import qutlass_ops as ops
+    dev = torch.device("cuda:0")
+    m, n, k = 3, 2048, 4096
+    aq, asf = _quantized(m, k, fmt, 5)
+    bq, bsf = _quantized(n, k, fmt, 6, scale=0.02)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    al = torch.tensor([1.0 / 9.0 if fmt == "mx" else 1.0 / 100.0], device=dev)
+    bias = synth.weights(1, n, seed=8).to(dev).reshape(n)
+    res = synth.weights(m, n, seed=9).to(dev)
+    args = (t(aq), t(bq), ops.to_blocked(t(asf)), ops.to_blocked(t(bsf)), al, fmt)
+    y_mv = ops.matmul_fp4_blocked(*args, bias=bias, residual=res)
+    y_tc = ops.matmul_fp4_blocked(*args, bias=bias, residual=res, splits=1)
+    plain_mv = ops.matmul_fp4_blocked(*args)
+    torch.cuda.synchronize()
+    assert torch.equal(y_mv, ((plain_mv + bias) + res))                 # the epilogue is the separate bf16 adds
+    d = (y_mv.float() - y_tc.float()).abs()
+    assert float(d.max()) <= float(y_tc.float().abs().max()) * 2.0 ** -7
+    assert float((d > 0).float().mean()) < 0.05

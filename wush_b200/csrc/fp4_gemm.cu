@@ -30,6 +30,7 @@
 
 #include "../../include/wush_b200.h"
 #include "common.cuh"
+#include "fp4_gemv.cuh"
 #include "sm100.cuh"
 
 namespace wush {
@@ -1056,6 +1057,12 @@ static int gemm_launch(bool nv, const uint8_t* a, const uint8_t* b, const uint8_
       p.y_peer[p.n_peers++] = (__nv_bfloat16*)shard->y_all[(shard->rank + i) % shard->world];
     force_splits = 1;      // partial tiles have no peer path: the sharded GEMM always runs unsplit
   }
+  // decode: with a handful of activation rows the product is one pass over the weight bytes, done by the
+  // matrix-vector kernel (no K splits, tensor maps or tensor memory); callers that force a split count, shard the
+  // output or stack K shards keep the tensor-core path
+  if (force_splits <= 0 && !shard && !(epi && epi->a_shards > 1) && m <= gemv::max_rows() && k <= gemv::max_k())
+    return gemv::launch(nv, a, b, sfa, sfb, alpha, p.bias, p.residual, p.ldr ? p.ldr : n, y, p.ldy, (int)m, (int)n, (int)k,
+                        stream);
   p.m_blocks = (int)((m + BM - 1) / BM);
   p.n_blocks = (int)((n + BN - 1) / BN);
   p.k_blocks = (int)((k + BK - 1) / BK);
