@@ -46,6 +46,12 @@ extern "C" {
 #define WUSH_QUANT_ROUND_BF16 1 /* round the transformed values to bf16 before quantizing, as the
                                    reference's runtime module does between its einsum and its
                                    quantizer (src/utils/wush_utils.py:140-149) */
+#define WUSH_QUANT_WIDE_MATRIX 2 /* `mat` is one square bf16 matrix [mat_cols, mat_cols] shared by every block of
+                                   mat_cols channels, wider than the quantization group: mat_cols 64 or 128 (and 32
+                                   for NVFP4); cols % mat_cols == 0.  y_block = x_block @ mat, then groups of 32 / 16
+                                   as usual: the shared Hadamard sizes of FPQuantConfig.hadamard_group_size
+                                   (inference_lib/src/fp_quant/utils/config.py:35-50).  Not with ROUND_BF16, the
+                                   debug or the strided entry. */
 
 /* quantization formats of the entry points that take a `format` argument */
 #define WUSH_FORMAT_MXFP4 0 /* groups of 32, E8M0 scales */

@@ -339,6 +339,17 @@ def fused_transform_quant(x: np.ndarray, mat: np.ndarray, fmt: str, round_bf16: 
     return out
 
 
+def wide_transform(x: np.ndarray, mat: np.ndarray) -> np.ndarray:
+    """y_block = x_block @ mat for consecutive blocks of n = mat.shape[0] channels, n any multiple of the scale group
+    (the shared Hadamard sizes 64 / 128 of inference_lib/src/fp_quant/utils/config.py:35-50).  This is the first step of
+    the reference's Triton kernels (inference_lib/src/fp_quant/module/triton/mxfp4.py:56-59: reshape to
+    (-1, hadamard_dim), tl.dot with the matrix); the result is regrouped by 32 / 16 for the scales afterwards.
+    float64 in, float64 out."""
+    x = np.asarray(x, dtype=np.float64)
+    n = mat.shape[0]
+    return (x.reshape(-1, n) @ np.asarray(mat, dtype=np.float64)).reshape(x.shape)
+
+
 #: Gaussian-optimal scale of the "quest" method (inference_lib/src/fp_quant/module/pseudoquant_linear_fns.py:21)
 QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0
 

@@ -216,9 +216,15 @@ def quest_vectors(root: str) -> None:
         clip = torch.empty(x.shape, dtype=torch.bool)
         n = x.numel()
         kernel[((n + 1023) // 1024,)](x_ptr=x, hadamard_matrix_ptr=had.contiguous(), output_ptr=out, clip_mask_ptr=clip,
-                                      n_elements=n, hadamard_dim=32, group_size=32, gaussian_scale=gaussian_scale,
+                                      n_elements=n, hadamard_dim=had.shape[0], group_size=32, gaussian_scale=gaussian_scale,
                                       quest=quest, WRITE_CLIP=True, BLOCK_SIZE=1024)
         return out.numpy().copy(), clip.numpy().copy()
+
+    def sylvester(n: int) -> torch.Tensor:
+        h = torch.tensor([[1.0]])
+        while h.shape[0] < n:
+            h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+        return h / n ** 0.5
 
     g = torch.Generator().manual_seed(777)
     bf = lambda t: t.to(torch.bfloat16).to(torch.float32)
@@ -235,7 +241,10 @@ def quest_vectors(root: str) -> None:
         h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
     had = bf(h / 32 ** 0.5)
     out = {"x": x.numpy(), "hadamard": had.numpy()}
-    for name, mat in (("identity", torch.eye(32)), ("hadamard", had)):
+    # transforms wider than the scale group: hadamard_group_size 64 and 128 (inference_lib/src/fp_quant/utils/config.py:44)
+    had64, had128 = bf(sylvester(64)), bf(sylvester(128))
+    out["hadamard64"], out["hadamard128"] = had64.numpy(), had128.numpy()
+    for name, mat in (("identity", torch.eye(32)), ("hadamard", had), ("hadamard64", had64), ("hadamard128", had128)):
         for quest, gsc in ((True, 2.92247856 / 6.0), (False, 3.0 / 4.0)):
             o, c = run(x, mat, quest, gsc)
             tag = f"{name}_{'quest' if quest else 'absmax'}"

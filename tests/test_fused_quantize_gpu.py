@@ -216,7 +216,7 @@ def test_pseudo_quant_wrappers_match_oracle_dequantization():
             got, mask = pq.mxfp4_forward_kernel_wrapper(x.to(dev).reshape(2, 48, 512), hm, return_clip_mask=True, quest=False)
             assert mask.dtype == torch.bool and bool(mask.all()) and mask.shape == got.shape
             with pytest.raises(NotImplementedError):
-                pq.mxfp4_forward_kernel_wrapper(x.to(dev), hm)          # quest=True is the reference's default
+                pq.mxfp4_forward_kernel_wrapper(x.to(dev), hm)          # the defaults: quest with the abs-max constant 3/4
         else:
             got = pq.nvfp4_forward_kernel_wrapper(x.to(dev).reshape(2, 48, 512), hm, torch.tensor(10.0, device=dev))
         assert got.shape == (2, 48, 512) and got.dtype == torch.bfloat16
@@ -360,3 +360,64 @@ def test_quest_against_triton_golden():
         assert np.mean(clip.cpu().numpy() != d[f"{name}_quest_clip"]) < 1e-3
     with pytest.raises(NotImplementedError):
         pseudo_quant.mxfp4_forward_kernel_wrapper(x.to(dev), torch.eye(32, device=dev), quest=True)   # 3/4 with quest
+
+
+# ---- shared transforms wider than the scale group (hadamard_group_size 64 / 128; 32 for NVFP4) -------------------
+
+def _sylvester(n):
+    h = np.ones((1, 1))
+    while h.shape[0] < n:
+        h = np.block([[h, h], [h, -h]])
+    return synth.bf16_to_f64(synth.to_bf16_tensor(h / np.sqrt(n)))
+
+
+@pytest.mark.parametrize("fmt,n", [("mx", 64), ("mx", 128), ("nv", 32), ("nv", 64), ("nv", 128)])
+@pytest.mark.parametrize("rows,cols", [(64, 128), (333, 4096), (130, 4096 + 128), (1, 256)])
+@pytest.mark.parametrize("blocked", [False, True])
+def test_wide_shared_matrix_matches_oracle(fmt, n, rows, cols, blocked):
+    """x_block @ H_n in fp32 by the kernel, in float64 (rounded once to float32) by the oracle, then the same
+    quantizer: scale bytes and codes within the tie budget.  Also a dense random 'rotation' in place of the
+    Hadamard matrix, since nothing in the kernel assumes +-c entries."""
+    ops = _ops()
+    dev = torch.device("cuda:0")
+    x = synth.activations(rows, cols, seed=rows + cols + n)
+    for mat in (_sylvester(n), synth.bf16_to_f64(synth.to_bf16_tensor(
+            np.linalg.qr(np.random.default_rng(n).standard_normal((n, n)))[0]))):
+        gs = torch.tensor([10.0], device=dev) if fmt == "nv" else None
+        q, sf = ops._quantize(x.to(dev), synth.to_bf16_tensor(mat).to(dev), fmt, gs, sf_layout=1 if blocked else 0)
+        torch.cuda.synchronize()
+        y = wo.wide_transform(synth.bf16_to_f64(x), mat).astype(np.float32).astype(np.float64)
+        ref = wo.rtn_xxfp4(y, FMT[fmt])
+        g = GROUP[fmt]
+        keep = ~np.isnan(ref["fake_quant"]).any(axis=1)
+        if blocked:
+            assert mismatch_fraction(np_u8(sf).reshape(-1), wo.to_blocked(ref["scale_quant"]).reshape(-1)) <= 1e-3
+        else:
+            assert mismatch_fraction(np_u8(sf)[:rows, : cols // g][keep], ref["scale_quant"][keep]) <= 1e-3
+        # the fp32 sums of 64 / 128 terms differ from the float64 ones in the last bits: values that sit on a rounding
+        # boundary or on a power of two of the group maximum move a code or a scale (budget 1e-3)
+        assert mismatch_fraction(canon_codes(np_u8(q)[keep]), canon_codes(ref["e2m1"][keep])) <= 1e-3
+
+
+def test_wide_matrix_against_triton_golden_and_quest():
+    """hadamard_group_size 64 and 128 on the committed outputs of the reference's Triton kernel, both methods,
+    through the wrapper that mirrors the reference's; and the op-level API with a 128-wide Hadamard."""
+    import os
+    from wush_b200 import pseudo_quant
+    ops = _ops()
+    d = np.load(os.path.join(os.path.dirname(__file__), "golden", "quest_vectors.npz"))
+    dev = torch.device("cuda:0")
+    x = torch.from_numpy(d["x"]).to(torch.bfloat16).to(dev)
+    for name in ("hadamard64", "hadamard128"):
+        mat = torch.from_numpy(d[name]).to(dev, torch.bfloat16)
+        for quest, gsc in ((True, 2.92247856 / 6.0), (False, 0.75)):
+            out, clip = pseudo_quant.mxfp4_forward_kernel_wrapper(x, mat, return_clip_mask=True, quest=quest, gaussian_scale=gsc)
+            tag = f"{name}_{'quest' if quest else 'absmax'}"
+            want = torch.from_numpy(d[tag + "_out"]).to(torch.bfloat16).float().numpy()
+            got = out.float().cpu().numpy()
+            assert np.mean(got != want) < 0.03, (tag, np.mean(got != want))        # ties + sum order
+            assert np.mean(clip.cpu().numpy() != d[tag + "_clip"]) < 2e-3
+    q, sf, mask = ops.fused_quantize_mx_op(x, torch.from_numpy(d["hadamard128"]).to(dev, torch.bfloat16), "quest", True)
+    assert q.shape == (64, 64) and mask.shape == (64, 16)
+    with pytest.raises(NotImplementedError):
+        ops.fused_quantize_mx_op(x[:, :64], torch.from_numpy(d["hadamard128"]).to(dev, torch.bfloat16), "abs_max", False)

@@ -247,3 +247,32 @@ def test_single_layer_pipeline_at_4096_through_a_checkpoint_file(tmp_path):
     want = ref_x @ ref_w["fake_quant"].T
     got = y_mem.double().cpu().numpy()[:, rows]
     assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
+
+
+@pytest.mark.parametrize("fmt,size,init", [("mxfp4", 128, "hadamard"), ("mxfp4", 64, "gsr"), ("nvfp4", 64, "hadamard")])
+def test_layer_with_a_transform_wider_than_the_scale_group(fmt, size, init):
+    """hadamard_group_size 64 / 128 (and the sequency-ordered "gsr" columns): the layer quantizes its weight and its
+    activations with one shared square matrix per block of that many channels; scales stay per 32 / 16 channels.
+    The output equals the product of the two dequantized operands (rotations cancel: H H^T = I up to bf16)."""
+    from oracle import wush_oracle as wo
+    from wush_b200.linear import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    dev = torch.device("cuda:0")
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype(fmt), hadamard_group_size=size, transform_init=init)
+    layer = FPQuantLinear(1024, 256, cfg, bias=False, device=dev)
+    w = synth.weights(256, 1024, seed=26)
+    layer.weight.data.copy_(w.to(dev))
+    layer.pre_forward()
+    group = 32 if fmt == "mxfp4" else 16
+    assert layer.forward_hadamard_matrix.shape == (size, size) and layer.scales.shape == (256, 1024 // group)
+    mat = synth.bf16_to_f64(layer.forward_hadamard_matrix.cpu())
+    assert np.allclose(mat @ mat.T, np.eye(size), atol=2e-2)
+    if init == "gsr":                      # column j changes sign j times
+        assert np.array_equal((np.diff(np.sign(mat), axis=0) != 0).sum(axis=0), np.arange(size))
+    x = synth.activations(96, 1024, seed=27)
+    y = layer(x.to(dev)).double().cpu().numpy()
+    deq = lambda t: wo.rtn_xxfp4(wo.wide_transform(synth.bf16_to_f64(t), mat).astype(np.float32).astype(np.float64),
+                                 fmt)["fake_quant"]
+    want = deq(x) @ deq(w).T
+    assert np.linalg.norm(y - want) <= 1e-2 * np.linalg.norm(want)
+    exact = synth.bf16_to_f64(x) @ synth.bf16_to_f64(w).T
+    assert np.linalg.norm(y - exact) / np.linalg.norm(exact) < 0.25

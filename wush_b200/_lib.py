@@ -21,6 +21,7 @@ ERRORS = {
 
 SF_ROW_MAJOR, SF_BLOCKED = 0, 1
 QUANT_ROUND_BF16 = 1
+QUANT_WIDE_MATRIX = 2
 HESSIAN_LOWER_ONLY = 1
 HESSIAN_INPUT_F32 = 2
 HESSIAN_OVERWRITE = 4

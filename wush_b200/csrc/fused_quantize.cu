@@ -239,10 +239,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 // RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
 // the transformed values.  PRO: scale the activations by row_scale / col_scale first (see QuantParams).
 // QUEST (MXFP4 only): standard-deviation scale with clipping instead of the absolute-maximum scale.
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false>
-__global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
-  constexpr int TD = NV ? 16 : 32;       // transform size == quantization group
+// W = 0: the transform is as wide as the quantization group (per-group or shared matrix).  W = 1, 2, 4: one dense
+// square matrix of 32 W channels shared by every block of 32 W channels (Hadamard sizes 64 and 128, and 32 for
+// NVFP4): the W warps of a block each contract all W chunks of the block, reading the other warps' activation tiles
+// from the ring (one more block barrier per tile) and keeping W times the matrix fragments in registers.
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0>
+__global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
+  constexpr int TD = NV ? 16 : 32;       // quantization group (and transform size when W == 0)
   constexpr int GPC = kChunk / TD;       // scale groups per chunk
+  constexpr int KC = W ? W : 1;          // chunks contracted per output chunk
+  constexpr int kMatRows = W ? 32 * W : 32;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   // [0, kRingBytes)   activation ring: per stage and warp a 32-row x 64-byte tile of the warp's chunk, the
   //                   16-byte pieces of a row XOR-swizzled by (row/2)%4 so ldmatrix reads without conflicts
@@ -250,13 +256,13 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   //                   into MMA fragment order (see below); NVFP4 chunks are block-diagonal 32x32
   // then              two staging buffers for a tile's packed codes and scale bytes
   __nv_bfloat16* smat = reinterpret_cast<__nv_bfloat16*>(smem_raw + kRingBytes);
-  uint8_t* sout = smem_raw + kRingBytes + kMatBytes;
+  uint8_t* sout = smem_raw + kRingBytes + kMatRows * kMatStride * 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q4 = lane & 3;
   const int64_t slab_col0 = (int64_t)blockIdx.x * kSlab;
   const int64_t col0 = slab_col0 + warp * kChunk;
-  const bool shared_mat = p.mat_cols == TD;
+  const bool shared_mat = W == 0 && p.mat_cols == TD;
 
   // even split of the 32-row tiles over the row splits (every split gets at least one tile)
   const int tiles_total = (int)((p.rows + kTileRows - 1) / kTileRows);
@@ -307,7 +313,18 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   // columns 8j ..) read with ldmatrix.trans then hands lane (g, q) the pair
   // M[16ks+8h+2q+{0,1}][8(g/2)+2j+(g%2)]: the B fragment of the column-permuted MMA described at
   // the top of this file.
-  {
+  if (W) {
+    // dense (32 W) x (32 W) matrix: every 32 x 32 sub-block goes into the same permuted layout
+    constexpr int n = 32 * KC, vec_per_row = n / 8;
+    for (int idx = threadIdx.x; idx < n * vec_per_row; idx += blockDim.x) {
+      const int km = idx / vec_per_row, n8 = (idx % vec_per_row) * 8;
+      const uint4 v = *reinterpret_cast<const uint4*>(p.mat + (int64_t)km * n + n8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint32_t*>(&smat[km * kMatStride + (n8 & ~31) + 8 * j + 2 * ((n8 & 31) >> 3)]) = w[j];
+    }
+  } else {
     const int ncols = shared_mat ? TD : kSlab;
     const int vec_per_row = ncols / 8;
     for (int idx = threadIdx.x; idx < TD * vec_per_row; idx += blockDim.x) {
@@ -352,19 +369,23 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
   __syncthreads();
 
   // ---- this lane's matrix fragments: bfrag[j][ks][h] ---------------------------------------
-  uint32_t bfrag[4][2][2];
+  uint32_t bfrag[KC][4][2][2];
   {
-    const int cbase = shared_mat ? 0 : warp * kChunk;
+    // W: this warp's output chunk is chunk (warp % W) of its block; input chunk kc supplies rows 32 kc .. 32 kc + 31
+    const int cbase = W ? (warp % KC) * kChunk : (shared_mat ? 0 : warp * kChunk);
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
+    for (int kc = 0; kc < KC; ++kc) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t r[4];
-        const int srow = 16 * ks + 8 * h + (lane & 7);
-        const int scol = cbase + 8 * (lane >> 3);
-        ldmatrix_x4_trans(r, smem_base + kRingBytes + (srow * kMatStride + scol) * 2);
+      for (int ks = 0; ks < 2; ++ks) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) bfrag[j][ks][h] = r[j];
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[4];
+          const int srow = 32 * kc + 16 * ks + 8 * h + (lane & 7);
+          const int scol = cbase + 8 * (lane >> 3);
+          ldmatrix_x4_trans(r, smem_base + kRingBytes + (srow * kMatStride + scol) * 2);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bfrag[kc][j][ks][h] = r[j];
+        }
       }
     }
   }
@@ -417,16 +438,19 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
     uint8_t* out_q = sout + (t & 1) * (kOutBytes + kSfBytes);
     uint8_t* out_sf = out_q + kOutBytes;
 
+    if (W) __syncthreads();  // the tile's chunks were copied by eight different warps
     if (active) {
-      __syncwarp();  // the tile was copied by all lanes of this warp
+      if (!W) __syncwarp();  // the tile was copied by all lanes of this warp
       // A fragments: rows (lane%8) + 8*((lane/8)%2) of a 16-row tile, 16-byte piece (lane/16) + 2ks
       const uint32_t tile = smem_base + use_stage_off;
       use_stage_off = use_stage_off + kStageBytes == kRingBytes ? 0u : use_stage_off + kStageBytes;
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {  // two 16-row MMA tiles: rows g+16mt and g+8+16mt
         uint32_t a0[4], a1[4];
-        ldmatrix_x4(a0, tile + a_off[mt][0]);
-        ldmatrix_x4(a1, tile + a_off[mt][1]);
+        // W: start with the first chunk of this warp's block (the ring regions of the warps are kStageBytes / kWarps apart)
+        const uint32_t tile0 = W ? tile - (warp % KC) * (kStageBytes / kWarps) : tile;
+        ldmatrix_x4(a0, tile0 + a_off[mt][0]);
+        ldmatrix_x4(a1, tile0 + a_off[mt][1]);
         if (PRO) {
           // registers 0/2 hold row g + 16mt, registers 1/3 row g + 8 + 16mt; 0/1 channels 2q.., 2/3 channels 8 + 2q..
           const float rs0 = p.row_scale[min(r0 + g + 16 * mt, last_row)];
@@ -447,8 +471,18 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
         float acc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          mma_bf16_16816_zero(acc[j], a0[0], a0[1], a0[2], a0[3], bfrag[j][0][0], bfrag[j][0][1]);
-          mma_bf16_16816(acc[j], a1[0], a1[1], a1[2], a1[3], bfrag[j][1][0], bfrag[j][1][1]);
+          mma_bf16_16816_zero(acc[j], a0[0], a0[1], a0[2], a0[3], bfrag[0][j][0][0], bfrag[0][j][0][1]);
+          mma_bf16_16816(acc[j], a1[0], a1[1], a1[2], a1[3], bfrag[0][j][1][0], bfrag[0][j][1][1]);
+        }
+#pragma unroll
+        for (int kc = 1; kc < KC; ++kc) {  // the other chunks of the block (wide matrices only)
+          ldmatrix_x4(a0, tile0 + kc * (kStageBytes / kWarps) + a_off[mt][0]);
+          ldmatrix_x4(a1, tile0 + kc * (kStageBytes / kWarps) + a_off[mt][1]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            mma_bf16_16816(acc[j], a0[0], a0[1], a0[2], a0[3], bfrag[kc][j][0][0], bfrag[kc][j][0][1]);
+            mma_bf16_16816(acc[j], a1[0], a1[1], a1[2], a1[3], bfrag[kc][j][1][0], bfrag[kc][j][1][1]);
+          }
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -521,7 +555,7 @@ __global__ void __launch_bounds__(kWarps * 32, WUSH_Q_MINBLOCKS) fused_quantize_
 // Grid: x = slabs, y = row splits.  Every CTA takes an equal share (+-1) of the 32-row tiles.
 // The number of row splits is the largest that keeps all CTAs co-resident in `waves` waves of
 // (SMs x CTAs per SM), so the last wave is not a mostly empty tail.
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false>
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
   const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
@@ -530,15 +564,15 @@ static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   // 4930/5170/5200).  WUSH_B200_QUANT_WAVES overrides the choice.
   static const int waves_env = env_int("WUSH_B200_QUANT_WAVES", 0);
   const int waves = waves_env > 0 ? waves_env : (slabs <= 16 ? 1 : (slabs <= 32 ? 2 : 3));
-  const int64_t resident = (int64_t)sm_count() * WUSH_Q_MINBLOCKS;
+  const int64_t resident = (int64_t)sm_count() * (W ? 1 : WUSH_Q_MINBLOCKS);
   int64_t splits = (resident * waves) / slabs;
   if (splits < 1) splits = 1;
   if (splits > tiles) splits = tiles;
   if (splits > 65535) splits = 65535;
   p.row_splits = (int)splits;
   dim3 grid((unsigned)slabs, (unsigned)splits);
-  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO, QUEST>;
-  constexpr int smem = kQuantSmem;
+  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO, QUEST, W>;
+  constexpr int smem = kQuantSmem + (W ? (32 * W - 32) * kMatStride * 2 : 0);
   static PerDevice attr_set;     // per instantiation and device
   const int rc = opt_in_smem(attr_set, kern, smem);
   if (rc != 0) return rc;
@@ -565,13 +599,42 @@ static int check_quant_args(bool nv, const void* x, const void* mat, int64_t mat
   const int g = nv ? 16 : 32;
   if (!x || !mat || !q || !sf || (nv && !gs)) return WUSH_ERR_NULL_POINTER;
   if (rows < 0 || cols <= 0 || cols % 32 != 0) return WUSH_ERR_BAD_SHAPE;
-  if (mat_cols != cols && mat_cols != g) return WUSH_ERR_BAD_SHAPE;
+  if (flags & ~(WUSH_QUANT_ROUND_BF16 | WUSH_QUANT_WIDE_MATRIX)) return WUSH_ERR_BAD_FLAG;
+  if (flags & WUSH_QUANT_WIDE_MATRIX) {
+    // one square matrix of mat_cols channels, wider than (or, for NVFP4, twice) the quantization group
+    if (flags & WUSH_QUANT_ROUND_BF16) return WUSH_ERR_BAD_FLAG;
+    if (mat_cols != 64 && mat_cols != 128 && !(nv && mat_cols == 32)) return WUSH_ERR_BAD_SHAPE;
+    if (cols % mat_cols != 0) return WUSH_ERR_BAD_SHAPE;
+    if ((uintptr_t)mat & 15) return WUSH_ERR_BAD_ALIGNMENT;
+  } else if (mat_cols != cols && mat_cols != g) {
+    return WUSH_ERR_BAD_SHAPE;
+  }
   if (sf_cols % 4 != 0 || sf_cols < cols / g) return WUSH_ERR_BAD_SHAPE;
   if (sf_layout != WUSH_SF_ROW_MAJOR && sf_layout != WUSH_SF_BLOCKED) return WUSH_ERR_BAD_FLAG;
-  if (flags & ~WUSH_QUANT_ROUND_BF16) return WUSH_ERR_BAD_FLAG;
   if (((uintptr_t)x & 15) || ((uintptr_t)q & 15) || ((uintptr_t)sf & 3)) return WUSH_ERR_BAD_ALIGNMENT;
   if (mat_cols == cols && ((uintptr_t)mat & 15)) return WUSH_ERR_BAD_ALIGNMENT;
   return WUSH_OK;
+}
+
+// Wide shared matrices (WUSH_QUANT_WIDE_MATRIX): production instantiations only.
+template <bool NV, bool QUEST>
+static int launch_quant_wide(const QuantParams& p, cudaStream_t stream) {
+  if (const int rc100 = require_sm100()) return rc100;
+  const bool bl = p.sf_layout == WUSH_SF_BLOCKED;
+  switch (p.mat_cols) {
+    case 32:
+      if (!NV) return WUSH_ERR_BAD_SHAPE;
+      return bl ? launch_quant_t<NV, false, false, true, false, QUEST, NV ? 1 : 2>(p, stream)
+                : launch_quant_t<NV, false, false, false, false, QUEST, NV ? 1 : 2>(p, stream);
+    case 64:
+      return bl ? launch_quant_t<NV, false, false, true, false, QUEST, 2>(p, stream)
+                : launch_quant_t<NV, false, false, false, false, QUEST, 2>(p, stream);
+    case 128:
+      return bl ? launch_quant_t<NV, false, false, true, false, QUEST, 4>(p, stream)
+                : launch_quant_t<NV, false, false, false, false, QUEST, 4>(p, stream);
+    default:
+      return WUSH_ERR_BAD_SHAPE;
+  }
 }
 
 }  // namespace wush
@@ -586,6 +649,7 @@ extern "C" int wush_fused_quantize_mx(const void* x, const void* mat, int64_t ma
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
                 sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
+  if (flags & WUSH_QUANT_WIDE_MATRIX) return launch_quant_wide<false, false>(p, (cudaStream_t)stream);
   return launch_quant<false, false>(p, (cudaStream_t)stream);
 }
 
@@ -599,6 +663,7 @@ extern "C" int wush_fused_quantize_mx_quest(const void* x, const void* mat, int6
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, nullptr, q, sf, nullptr,
                 sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr,
                 clip_mask};
+  if (flags & WUSH_QUANT_WIDE_MATRIX) return launch_quant_wide<false, true>(p, (cudaStream_t)stream);
   const bool bl = sf_layout == WUSH_SF_BLOCKED;
   if (p.round_bf16)
     return bl ? launch_quant_t<false, false, true, true, false, true>(p, (cudaStream_t)stream)
@@ -615,6 +680,7 @@ extern "C" int wush_fused_quantize_nv(const void* x, const void* mat, int64_t ma
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, nullptr,
                 sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};
+  if (flags & WUSH_QUANT_WIDE_MATRIX) return launch_quant_wide<true, false>(p, (cudaStream_t)stream);
   return launch_quant<true, false>(p, (cudaStream_t)stream);
 }
 
@@ -627,6 +693,7 @@ extern "C" int wush_fused_quantize_debug(int fmt, const void* x, const void* mat
   int rc = check_quant_args(fmt == 1, x, mat, mat_cols, global_scale, q, sf, sf_cols, sf_layout, rows, cols, flags);
   if (rc != WUSH_OK) return rc;
   if ((uintptr_t)transformed & 15) return WUSH_ERR_BAD_ALIGNMENT;
+  if (flags & WUSH_QUANT_WIDE_MATRIX) return WUSH_ERR_BAD_FLAG;
   if (rows == 0) return WUSH_OK;
   QuantParams p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)mat, mat_cols, global_scale, q, sf, transformed,
                 sf_cols, sf_layout, cols, cols / 2, 0, rows, cols, 0, (flags & WUSH_QUANT_ROUND_BF16) ? 1 : 0, nullptr, nullptr};

@@ -35,7 +35,7 @@ class FPQuantConfig:
     store_master_weights: bool = False
     hadamard_group_size: int = 32
     pseudoquantization: bool = False
-    transform_init: str = "hadamard"            # "hadamard" | "identity" | "wush"
+    transform_init: str = "hadamard"            # "hadamard" | "identity" | "gsr" | "wush"
     modules_to_not_convert: List[str] = field(default_factory=lambda: ["lm_head"])
 
 
@@ -48,9 +48,13 @@ def validate_config(config: FPQuantConfig) -> None:
         # the reference's per-group op ignores the method (qutlass_ops.py:110-125) while its layer sets the global
         # scales for it (linear.py:207-211): the two do not fit together there either
         raise NotImplementedError("forward_method='quest' needs a shared square transform (hadamard or identity)")
-    want = 32 if config.forward_dtype == FPQuantDtype.MXFP4 else 16
-    if config.hadamard_group_size != want:
-        raise NotImplementedError(f"{config.forward_dtype.value} needs hadamard_group_size == {want} here")
+    # inference_lib/src/fp_quant/utils/config.py:35-50: 32 / 64 / 128 for MXFP4, also 16 for NVFP4; a per-group (WUSH)
+    # matrix is always as wide as the quantization group
+    want = (32, 64, 128) if config.forward_dtype == FPQuantDtype.MXFP4 else (16, 32, 64, 128)
+    if config.hadamard_group_size not in want:
+        raise ValueError(f"{config.forward_dtype.value} can only be used with hadamard_group_size in {list(want)}")
+    if config.transform_init == "wush" and config.hadamard_group_size != want[0]:
+        raise NotImplementedError(f"per-group WUSH matrices are {want[0]} wide for {config.forward_dtype.value}")
     if config.store_master_weights or config.pseudoquantization or config.backward_dtype != FPQuantDtype.BF16:
         raise NotImplementedError("inference only: no master weights, pseudo-quantization or quantized backward")
 
@@ -94,7 +98,10 @@ class FPQuantLinear(nn.Module):
         self.weight = nn.Parameter(torch.empty((out_features, in_features), **kw), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(out_features, **kw), requires_grad=False) if bias else None
         self.register_buffer("qweight", torch.empty(out_features, in_features // 2, dtype=torch.uint8, device=device))
-        self.register_buffer("scales", torch.empty(out_features, in_features // g, dtype=torch.uint8, device=device))
+        qg = 32 if config.forward_dtype == FPQuantDtype.MXFP4 else 16     # scale group, whatever the transform size
+        if in_features % g != 0:
+            raise ValueError(f"in_features must be divisible by the hadamard group size ({g})")
+        self.register_buffer("scales", torch.empty(out_features, in_features // qg, dtype=torch.uint8, device=device))
         # 3.0 whenever the method is abs_max, for both formats, like the reference's pre_forward (linear.py:206-217:
         # its abs_max branch comes before the NVFP4 one); exported WUSH checkpoints carry their own value (10.0 for
         # NVFP4, wush_gptq.py:588) and overwrite it through the state dict.  Buffers in the module dtype, as there.
@@ -132,10 +139,15 @@ class FPQuantLinear(nn.Module):
             mat = _hadamard(g, dev, dt)
         elif cfg.transform_init == "identity":
             mat = torch.eye(g, device=dev, dtype=dt)
+        elif cfg.transform_init == "gsr":
+            # the Hadamard columns ordered by their number of sign changes (reference: get_gsr_matrix, linear.py:44-48)
+            h = _hadamard(g, dev, dt)
+            mat = h[:, torch.argsort(torch.diff(h, dim=0).ne(0).sum(dim=0))].contiguous()
         else:
             raise ValueError(f"Invalid transform init: {cfg.transform_init}")
         q, s = forward_quantize(self.weight.data, mat, self.weight_global_scale, cfg.forward_dtype, cfg.forward_method)
-        self.load_quantized(q, s[: self.out_features, : self.in_features // g], mat)
+        qg = 32 if cfg.forward_dtype == FPQuantDtype.MXFP4 else 16
+        self.load_quantized(q, s[: self.out_features, : self.in_features // qg], mat)
 
     @torch.no_grad()
     def load_quantized(self, qweight: torch.Tensor, scales: torch.Tensor, matrix: torch.Tensor,

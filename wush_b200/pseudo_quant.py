@@ -39,8 +39,8 @@ def mxfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor,
     """(dequantized tensor like x, clip mask | None).  x @ hadamard_matrix per 32-element group, E8M0 scale, E2M1
     values.  quest=False: abs-max scale, which never clips, so the mask is all True.  quest=True: the scale follows
     the group's standard deviation and the mask marks the values inside +-6 scales."""
-    if hadamard_matrix.shape[-1] != 32:
-        raise NotImplementedError("the transform must be 32 x 32 (one scale group)")
+    if hadamard_matrix.shape[-1] not in (32, 64, 128) or hadamard_matrix.shape[0] != hadamard_matrix.shape[-1]:
+        raise NotImplementedError("the transform must be square, 32, 64 or 128 wide")
     xf = _flat(x)
     mat = hadamard_matrix.to(device=x.device, dtype=torch.bfloat16)
     if quest:
@@ -64,8 +64,8 @@ def mxfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor,
 def nvfp4_forward_kernel_wrapper(x: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor) -> torch.Tensor:
     """Dequantized tensor like x: x @ hadamard_matrix per 16-element group, E4M3 scale of absmax * global_scale / 6,
     E2M1 values, divided by global_scale again."""
-    if hadamard_matrix.shape[-1] != 16:
-        raise NotImplementedError("the transform must be 16 x 16 (one scale group)")
+    if hadamard_matrix.shape[-1] not in (16, 32, 64, 128) or hadamard_matrix.shape[0] != hadamard_matrix.shape[-1]:
+        raise NotImplementedError("the transform must be square, 16, 32, 64 or 128 wide")
     xf = _flat(x)
     gs = global_scale.to(device=x.device, dtype=torch.float32).reshape(-1)[:1]
     q, sf = ops._quantize(xf, hadamard_matrix.to(device=x.device, dtype=torch.bfloat16), "nv", gs)

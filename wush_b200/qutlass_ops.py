@@ -57,10 +57,17 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
     rows, cols = x_flat.shape
     if cols % 32 != 0:
         raise ValueError(f"channels ({cols}) must be a multiple of 32")
-    if matrix.dim() != 2 or matrix.shape[0] != group or matrix.shape[1] not in (group, cols):
+    # a square matrix wider than the group: one Hadamard-type transform per block of n channels (n = 64, 128; 32 for nv)
+    wide = matrix.dim() == 2 and matrix.shape[0] == matrix.shape[1] and matrix.shape[0] > group
+    if wide:
+        if matrix.shape[0] not in (32, 64, 128) or cols % matrix.shape[0] != 0 or round_bf16:
+            raise NotImplementedError(
+                f"shared transform of shape {tuple(matrix.shape)} on {cols} channels: the size must be 64 or 128 (32 for "
+                f"nvfp4) and divide the channels; not with round_bf16")
+    elif matrix.dim() != 2 or matrix.shape[0] != group or matrix.shape[1] not in (group, cols):
         raise NotImplementedError(
-            f"transform matrix of shape {tuple(matrix.shape)}: supported are ({group}, {group}) shared and "
-            f"({group}, {cols}) per-group")
+            f"transform matrix of shape {tuple(matrix.shape)}: supported are ({group}, {group}) shared, "
+            f"({group}, {cols}) per-group and square shared matrices of 64 or 128 channels")
     x_flat = x_flat.contiguous()
     matrix = matrix.contiguous()
     q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x_flat.device)
@@ -68,7 +75,7 @@ def _quantize(x_flat: torch.Tensor, matrix: torch.Tensor, fmt: str, global_scale
     lib = _lib.load()
     if rows == 0:
         return q, sf
-    flags = _lib.QUANT_ROUND_BF16 if round_bf16 else 0
+    flags = (_lib.QUANT_ROUND_BF16 if round_bf16 else 0) | (_lib.QUANT_WIDE_MATRIX if wide else 0)
     with torch.cuda.device(x_flat.device):
         if quest:
             rc = lib.wush_fused_quantize_mx_quest(x_flat.data_ptr(), matrix.data_ptr(), matrix.shape[1], q.data_ptr(),
