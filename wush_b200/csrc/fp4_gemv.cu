@@ -251,13 +251,12 @@ __global__ void __launch_bounds__(WARPS * 32) fp4_gemv_kernel(const Params p) {
 template <bool NV, int M>
 static int launch_m(Params p, cudaStream_t stream) {
   const int units = p.k >> 5;
-  // Warps per pair of rows: enough warps in total to hide each other's latencies (a warp alone on its scheduler
-  // runs its few hundred dependent instructions at a seventh of the issue rate), and at most BATCH passes per warp
-  // so that all of a warp's loads are in flight at once.
+  // Warps per pair of rows: one, unless the k range needs more than BATCH passes of 32 units; then the passes are
+  // split over 2 or 4 warps so that all of a warp's loads are in flight at once.  (Splitting further to get more
+  // warps for small matrices measured no better: every CTA converts the whole activation row.)
   const int iters = (units + 31) >> 5;
   int split = 1;
-  while (split < WARPS && split * 2 <= iters && ((int64_t)(p.n / RW) * split < 4096 || (iters + split - 1) / split > BATCH))
-    split *= 2;
+  while (split < WARPS && (iters + split - 1) / split > BATCH) split *= 2;
   p.ksplit = split;
   const size_t smem = (size_t)M * units * (64 + (NV ? 8 : 4));
   auto kern = fp4_gemv_kernel<NV, M>;
