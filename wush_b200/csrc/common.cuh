@@ -88,4 +88,8 @@ inline int require_sm100() {
   return s == 1 ? WUSH_OK : WUSH_ERR_NOT_SM100;
 }
 
+// The quantize kernels' device-side timeout word (fused_quantize.cu), after the caller synchronized: 0 = clear,
+// WUSH_ERR_DEVICE_TIMEOUT = it was set (and has been cleared), > 0 = a cudaError_t.
+int quantize_timeout_fetch_and_clear();
+
 }  // namespace wush

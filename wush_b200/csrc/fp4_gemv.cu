@@ -126,16 +126,25 @@ __global__ void __launch_bounds__(WARPS * 32) fp4_gemv_kernel(const Params p) {
   // the first batch of weight loads goes out before the activations are staged
   uint4 bw[BATCH][RW];
   uint32_t sb[BATCH][RW];
+  // row-dependent parts of the addresses, once per warp: the codes of the row and its place inside the 128 x 4 scale atoms
+  const uint8_t* brow[RW];
+  const uint8_t* sfrow[RW];
+#pragma unroll
+  for (int r = 0; r < RW; ++r) {
+    const int row = min(row0 + r, p.n - 1);
+    brow[r] = p.b + (int64_t)row * ldb;
+    sfrow[r] = p.sfb + sf_off(row, 0, p.sf_cols);
+  }
   auto issue = [&](int it0) {
 #pragma unroll
     for (int j = 0; j < BATCH; ++j) {
       const int u = min((it0 + j) * 32 + lane, units - 1);
+      // scale group(s) of unit u: atom (g >> 2) is 512 bytes further, byte (g & 3) inside the row's word
+      const int sfo = NV ? (u >> 1) * 512 + (u & 1) * 2 : (u >> 2) * 512 + (u & 3);
 #pragma unroll
       for (int r = 0; r < RW; ++r) {
-        const int row = min(row0 + r, p.n - 1);
-        bw[j][r] = __ldg(reinterpret_cast<const uint4*>(p.b + (int64_t)row * ldb + (int64_t)u * 16));
-        sb[j][r] = NV ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.sfb + sf_off(row, 2 * u, p.sf_cols)))
-                      : (uint32_t)__ldg(p.sfb + sf_off(row, u, p.sf_cols));
+        bw[j][r] = __ldg(reinterpret_cast<const uint4*>(brow[r] + (int64_t)u * 16));
+        sb[j][r] = NV ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sfrow[r] + sfo)) : (uint32_t)__ldg(sfrow[r] + sfo);
       }
     }
   };

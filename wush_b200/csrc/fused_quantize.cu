@@ -18,9 +18,10 @@
 // rows; warp w owns chunk w and keeps that chunk's matrix fragments in 16 registers for the
 // CTA's lifetime.  Packed codes and scale bytes of a 32-row tile are staged in shared memory
 // and written out as full 128-byte lines (scattered 4-byte stores saturate the L1 data pipe).  Rows are walked 32 at a time; the activation loads run kStages-1 tiles ahead
-// of the math as 16-byte cp.async copies into lane-private shared-memory slots (each lane
-// reads back exactly the bytes it requested, so the ring needs no barrier and has no bank
-// conflicts), which keeps ~100 KB per SM in flight without holding registers.
+// of the math into a warp-private shared-memory ring, which keeps ~100 KB per SM in flight without holding
+// registers: one bulk tensor copy (TMA) per warp and tile in the production kernels, 16-byte cp.async copies
+// per lane in the other variants (each lane then reads back exactly the bytes it requested, so that ring needs
+// no barrier).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -29,6 +30,7 @@
 
 #include "../../include/wush_b200.h"
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace wush {
 
@@ -236,6 +238,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
                : "r"(smem_addr));
 }
 
+// set when a bounded wait on a bulk-copy barrier ran out (TMA variant); read and cleared by wush_fused_quantize_status
+__device__ int g_quant_timeout = 0;
+
 // RB: round transformed values to bf16 first.  BL: blocked scale layout.  DEBUG: also store
 // the transformed values.  PRO: scale the activations by row_scale / col_scale first (see QuantParams).
 // QUEST (MXFP4 only): standard-deviation scale with clipping instead of the absolute-maximum scale.
@@ -243,13 +248,17 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 // square matrix of 32 W channels shared by every block of 32 W channels (Hadamard sizes 64 and 128, and 32 for
 // NVFP4): the W warps of a block each contract all W chunks of the block, reading the other warps' activation tiles
 // from the ring (one more block barrier per tile) and keeping W times the matrix fragments in registers.
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0>
-__global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS) fused_quantize_kernel(const QuantParams p) {
+// TMA: the activation tiles are fetched by one elected lane per warp with cp.async.bulk.tensor (a 32 x 32 box of
+// the warp's chunk, 64-byte swizzle = the ring's layout) onto a per-warp, per-stage mbarrier, instead of by four
+// cp.async per lane.
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0, bool TMA = false>
+__global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS)
+fused_quantize_kernel(const __grid_constant__ CUtensorMap xmap, const QuantParams p) {
   constexpr int TD = NV ? 16 : 32;       // quantization group (and transform size when W == 0)
   constexpr int GPC = kChunk / TD;       // scale groups per chunk
   constexpr int KC = W ? W : 1;          // chunks contracted per output chunk
   constexpr int kMatRows = W ? 32 * W : 32;
-  extern __shared__ __align__(16) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   // [0, kRingBytes)   activation ring: per stage and warp a 32-row x 64-byte tile of the warp's chunk, the
   //                   16-byte pieces of a row XOR-swizzled by (row/2)%4 so ldmatrix reads without conflicts
   // then              the slab's matrices as 32 rows x (kSlab + 8) bf16, rows and columns permuted
@@ -285,7 +294,39 @@ __global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS) fused_q
   int issue_row = row_begin + g;                                   // first of this lane's 4 rows of the next tile
   const __nv_bfloat16* issue_ptr = xcol + (int64_t)issue_row * p.ldx;
   const int64_t row8 = 8 * p.ldx, row32 = 32 * p.ldx;             // element strides of 8 and 32 rows
+  // TMA variant: barriers [stage][warp] behind the staging buffers, then the CTA's abort word
+  constexpr int kTailOff = kRingBytes + kMatRows * kMatStride * 2 + 2 * (kOutBytes + kSfBytes);
+  const uint32_t bar0 = smem_base + kTailOff + warp * 8;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_raw + kTailOff + kStages * kWarps * 8);
+  if (TMA) {
+    // the swizzle of a bulk tensor copy follows the shared-memory address bits (period 512 bytes): the ring must
+    // start on such a boundary for the copies to land in the layout the ldmatrix offsets assume
+    if (smem_base & 511u) {
+      if (threadIdx.x == 0) atomicExch(&g_quant_timeout, 2);
+      return;
+    }
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < kStages; ++st) sm100::mbar_init(bar0 + st * kWarps * 8, 1);
+      sm100::mbar_init_fence();
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      sm100::tma_prefetch_desc(&xmap);
+    }
+    __syncwarp();
+  }
+  int issue_stage = 0;
   auto issue_tile = [&](int t) {
+    if (TMA) {
+      if (active && t < n_tiles && lane == 0) {
+        const uint32_t bar = bar0 + issue_stage * kWarps * 8;
+        sm100::mbar_arrive_expect_tx(bar, kStageBytes / kWarps);
+        sm100::tma_load_2d(smem_base + issue_stage * kStageBytes + warp * (kStageBytes / kWarps), &xmap, (int)col0,
+                           row_begin + t * kTileRows, bar);
+      }
+      issue_stage = issue_stage + 1 == kStages ? 0 : issue_stage + 1;
+      return;
+    }
     if (active && t < n_tiles) {
       const uint32_t dst = ring_wr + issue_stage_off;
       if (issue_row + 24 <= last_row) {
@@ -433,7 +474,13 @@ __global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS) fused_q
 
   for (int t = 0; t < n_tiles; ++t) {
     issue_tile(t + kStages - 1);
-    cp_async_wait<kStages - 1>();
+    if (TMA) {
+      // tile t sits in stage t % kStages; its barrier completes phase (t / kStages) & 1.  A wait that runs out
+      // raises the CTA's abort word (every later wait then returns at once) and the kernel reports it.
+      if (active) sm100::mbar_wait(bar0 + (t % kStages) * kWarps * 8, (uint32_t)(t / kStages) & 1u, abort_flag);
+    } else {
+      cp_async_wait<kStages - 1>();
+    }
     const int r0 = row_begin + t * kTileRows;
     uint8_t* out_q = sout + (t & 1) * (kOutBytes + kSfBytes);
     uint8_t* out_sf = out_q + kOutBytes;
@@ -550,12 +597,13 @@ __global__ void __launch_bounds__(kWarps * 32, W ? 1 : WUSH_Q_MINBLOCKS) fused_q
       }
     }
   }
+  if (TMA && threadIdx.x == 0 && *abort_flag) atomicExch(&g_quant_timeout, 1);
 }
 
 // Grid: x = slabs, y = row splits.  Every CTA takes an equal share (+-1) of the 32-row tiles.
 // The number of row splits is the largest that keeps all CTAs co-resident in `waves` waves of
 // (SMs x CTAs per SM), so the last wave is not a mostly empty tail.
-template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0>
+template <bool NV, bool DEBUG, bool RB, bool BL, bool PRO = false, bool QUEST = false, int W = 0, bool TMA = false>
 static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   const int64_t slabs = (p.cols + kSlab - 1) / kSlab;
   const int64_t tiles = (p.rows + kTileRows - 1) / kTileRows;
@@ -571,12 +619,19 @@ static int launch_quant_t(QuantParams p, cudaStream_t stream) {
   if (splits > 65535) splits = 65535;
   p.row_splits = (int)splits;
   dim3 grid((unsigned)slabs, (unsigned)splits);
-  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO, QUEST, W>;
-  constexpr int smem = kQuantSmem + (W ? (32 * W - 32) * kMatStride * 2 : 0);
+  auto kern = fused_quantize_kernel<NV, DEBUG, RB, BL, PRO, QUEST, W, TMA>;
+  constexpr int smem = kQuantSmem + (W ? (32 * W - 32) * kMatStride * 2 : 0) + (TMA ? kStages * kWarps * 8 + 16 : 0);
   static PerDevice attr_set;     // per instantiation and device
-  const int rc = opt_in_smem(attr_set, kern, smem);
+  int rc = opt_in_smem(attr_set, kern, smem);
   if (rc != 0) return rc;
-  kern<<<grid, kWarps * 32, smem, stream>>>(p);
+  CUtensorMap xmap = {};
+  if (TMA) {
+    // x as [rows][cols] bf16 with row stride ldx; box = one warp's 32 x 32 tile; 64-byte swizzle = the ring's layout
+    rc = make_tensor_map_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.x, (uint64_t)p.rows, (uint64_t)p.cols,
+                            (uint64_t)p.ldx * 2, kChunk, kTileRows, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != 0) return rc;
+  }
+  kern<<<grid, kWarps * 32, smem, stream>>>(xmap, p);
   return (int)cudaGetLastError();
 }
 
@@ -590,6 +645,10 @@ static int launch_quant(const QuantParams& p, cudaStream_t stream) {
     return bl ? launch_quant_t<NV, false, false, true, true>(p, stream) : launch_quant_t<NV, false, false, false, true>(p, stream);
   }
   if (rb) return bl ? launch_quant_t<NV, DEBUG, true, true>(p, stream) : launch_quant_t<NV, DEBUG, true, false>(p, stream);
+  static const int use_tma = env_int("WUSH_B200_QUANT_TMA", 1);
+  if (!DEBUG && use_tma && p.ldx % 8 == 0)
+    return bl ? launch_quant_t<NV, false, false, true, false, false, 0, true>(p, stream)
+              : launch_quant_t<NV, false, false, false, false, false, 0, true>(p, stream);
   return bl ? launch_quant_t<NV, DEBUG, false, true>(p, stream) : launch_quant_t<NV, DEBUG, false, false>(p, stream);
 }
 
@@ -635,6 +694,16 @@ static int launch_quant_wide(const QuantParams& p, cudaStream_t stream) {
     default:
       return WUSH_ERR_BAD_SHAPE;
   }
+}
+
+int quantize_timeout_fetch_and_clear() {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_quant_timeout, sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  if (v == 0) return 0;
+  const int zero = 0;
+  e = cudaMemcpyToSymbol(g_quant_timeout, &zero, sizeof(int));
+  return e != cudaSuccess ? (int)e : WUSH_ERR_DEVICE_TIMEOUT;
 }
 
 }  // namespace wush

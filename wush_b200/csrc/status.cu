@@ -34,9 +34,14 @@ extern "C" int wush_status_check(int* status_dev, void* stream) {
   cudaError_t e = cudaMemcpyAsync(&host, status_dev, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
-  if (host == 0) return WUSH_OK;
-  e = cudaMemsetAsync(status_dev, 0, sizeof(int), (cudaStream_t)stream);
-  if (e != cudaSuccess) return (int)e;
+  // the quantize kernels have no status argument: their bulk-copy waits report through a word inside the library
+  const int quant = wush::quantize_timeout_fetch_and_clear();
+  if (quant > 0) return quant;                       // a cudaError_t
+  if (host == 0 && quant == 0) return WUSH_OK;
+  if (host != 0) {
+    e = cudaMemsetAsync(status_dev, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+  }
   return WUSH_ERR_DEVICE_TIMEOUT;
 }
 
