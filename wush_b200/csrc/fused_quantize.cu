@@ -639,13 +639,16 @@ template <bool NV, bool DEBUG>
 static int launch_quant(const QuantParams& p, cudaStream_t stream) {
   if (const int rc100 = require_sm100()) return rc100;
   const bool rb = p.round_bf16 != 0, bl = p.sf_layout == WUSH_SF_BLOCKED;
+  static const int use_tma = env_int("WUSH_B200_QUANT_TMA", 1);   // 0: the cp.async ring everywhere
   if (p.row_scale != nullptr) {
     // the prologue exists for the production path only (no bf16 rounding of the transformed values, no debug output)
     if (DEBUG || rb) return WUSH_ERR_BAD_FLAG;
+    if (use_tma && p.ldx % 8 == 0)
+      return bl ? launch_quant_t<NV, false, false, true, true, false, 0, true>(p, stream)
+                : launch_quant_t<NV, false, false, false, true, false, 0, true>(p, stream);
     return bl ? launch_quant_t<NV, false, false, true, true>(p, stream) : launch_quant_t<NV, false, false, false, true>(p, stream);
   }
   if (rb) return bl ? launch_quant_t<NV, DEBUG, true, true>(p, stream) : launch_quant_t<NV, DEBUG, true, false>(p, stream);
-  static const int use_tma = env_int("WUSH_B200_QUANT_TMA", 1);
   if (!DEBUG && use_tma && p.ldx % 8 == 0)
     return bl ? launch_quant_t<NV, false, false, true, false, false, 0, true>(p, stream)
               : launch_quant_t<NV, false, false, false, false, false, 0, true>(p, stream);
