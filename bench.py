@@ -571,11 +571,11 @@ def bench_hessian(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind
         from wush_b200 import hessian as hz
         inner = hz._PeerBuffers.combine
 
-        def combine(self, hidden, a, b, channel):
+        def combine(self, hidden, a, b, channel, **kw):
             st = torch.cuda.current_stream(self.flat.device)
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record(st)
-            inner(self, hidden, a, b, channel)
+            inner(self, hidden, a, b, channel, **kw)
             ev[1].record(st)
             marks.append((channel, a, b, ev))
         hz._PeerBuffers.combine = combine

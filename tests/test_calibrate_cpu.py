@@ -188,7 +188,9 @@ def test_tile_panels_and_token_segments():
         p = tile_panels(n_tiles, per_wave)
         assert (p[0][0] == 0 and p[-1][1] == n_tiles) if n_tiles else p == []
         assert all(a[1] == b[0] for a, b in zip(p, p[1:])) and all(b > a for a, b in p)
-        assert all(a % per_wave == 0 for a, _ in p) and len(p) <= 7
+        assert all(a % per_wave == 0 for a, _ in p) and len(p) <= 7 + n_tiles // (3 * per_wave)
+        assert all(b - a <= 3 * per_wave for a, b in p)             # short enough to be combined out of the L2
+        assert len(tile_panels(n_tiles, per_wave, max_waves=0)) <= 7
         if n_tiles > per_wave:
             assert p[-1][1] - p[-1][0] <= per_wave              # only the last wave's combine is not hidden
     for tokens in (1, 32768, 49151, 49152, 65536, 262144, 70000):

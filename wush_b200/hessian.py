@@ -103,7 +103,8 @@ def token_segments(tokens: int) -> list[tuple[int, int]]:
     return out
 
 
-def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 7, ratio: float = 2.0) -> list[tuple[int, int]]:
+def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 7, ratio: float = 2.0,
+                max_waves: int = 3) -> list[tuple[int, int]]:
     """Cut the tile list [0, n_tiles) into launches whose cross-GPU combine can overlap the next launch.
 
     A launch works on `per_wave` tiles side by side, so a launch over a multiple of per_wave tiles wastes
@@ -111,7 +112,12 @@ def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 7, ratio: float =
     hides, so it is kept as small as the tile count allows.  The combine of a panel runs while the NEXT panel is
     multiplied and costs (measured, co-resident with the multiply kernel) a bit under half of the panel's own
     multiply time, so the panels before the last shrink geometrically towards the end (each `ratio` times the
-    next, whole waves): one wave before the last, then two, four, ... and the first panel takes what is left."""
+    next, whole waves): one wave before the last, then two, four, ... and the first panel takes what is left.
+    No panel is longer than `max_waves` waves (longer ones are cut into equal pieces): the combine reads the
+    panel's tiles back from every rank, and it runs several times faster while they still sit in the L2 caches
+    that the multiply kernel wrote them through (measured at hidden 14336: 0.8 us per tile for a panel of 75 MB
+    combined right after it was written, 4.7 us per tile for 113 MB that had been evicted by the next panel's
+    input stream -- enough for the side stream to fall behind the multiply kernel)."""
     per_wave = max(1, per_wave)
     waves = -(-n_tiles // per_wave)
     if waves <= 1 or max_panels <= 1:
@@ -126,6 +132,12 @@ def tile_panels(n_tiles: int, per_wave: int, max_panels: int = 7, ratio: float =
     if head > 0:
         sizes.append(head)
     sizes.reverse()
+    if max_waves >= 1:
+        capped = []
+        for w in sizes:
+            pieces = -(-w // max_waves)
+            capped += [w // pieces + (1 if i < w % pieces else 0) for i in range(pieces)]
+        sizes = capped
     cuts = [0]
     for w in sizes:
         cuts.append(cuts[-1] + w * per_wave)
@@ -183,7 +195,7 @@ class _PeerBuffers:
     def release(self) -> None:
         self._pool.setdefault(self.key, []).append(self)
 
-    def combine(self, hidden: int, tile_begin: int, tile_end: int, channel: int) -> None:
+    def combine(self, hidden: int, tile_begin: int, tile_end: int, channel: int, mirror: bool = True) -> None:
         """On the current stream: wait until every rank's partial sums of the tile range are complete, sum them
         across the ranks (scaled by 1 / total tokens), wait until every rank has delivered, rebuild the mirror
         image of the range locally.  The two waits are barriers the reduce and the mirror kernel run themselves
@@ -201,6 +213,17 @@ class _PeerBuffers:
                                               self.rank, self.world, hidden, tile_begin, tile_end, slots, self.epoch,
                                               status, stream)
         _lib.check(rc, "wush_hessian_peer_reduce")
+        if mirror:
+            self.mirror(hidden, tile_begin, tile_end, channel)
+
+    def mirror(self, hidden: int, tile_begin: int, tile_end: int, channel: int) -> None:
+        """On the current stream: wait until every rank has delivered the sums it owns (a barrier the mirror kernel
+        runs itself), then rebuild the mirror image of the tile range locally."""
+        lib = _lib.load()
+        dev = self.flat.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        status = _lib.status_word(dev).data_ptr()
+        slots = self.slot_table.data_ptr() if self.kernel_barrier else None
         if not self.kernel_barrier:
             self.handle.barrier(channel=channel)
         self.epoch += 1
@@ -379,7 +402,14 @@ class DistributedHessian:
             # WUSH_B200_HESSIAN_TILES_PER_PANEL overrides the device's wave size (small matrices in tests)
             per_wave = int(os.environ.get("WUSH_B200_HESSIAN_TILES_PER_PANEL", "0")) or int(lib.wush_hessian_tiles_per_wave())
         main = torch.cuda.current_stream(self.device)
-        panels = tile_panels(n_tiles, per_wave, self.panels)
+        panels = tile_panels(n_tiles, per_wave, self.panels,
+                             max_waves=int(os.environ.get("WUSH_B200_HESSIAN_PANEL_WAVES", "3")))
+        # With many panels the mirror images wait for one pass over the whole matrix at the end: beside the multiply
+        # kernel the mirror kernel crawls like the reduce kernel (measured at hidden 14336: together 1.5 ms for a
+        # panel the multiply kernel needs 0.75 ms for, so the side stream fell 0.4-0.7 ms behind), alone it moves
+        # the 2 x 411 MB in under 0.2 ms.  Small matrices (one or two panels) keep the per-panel mirror, which the
+        # next panel hides completely.
+        self._mirror_all = len(panels) > 2
         pb.side.wait_stream(main)               # the side stream starts behind everything issued so far
         for i, (a, b) in enumerate(panels):
             _kernel_accumulate_tiles(self.raw, xl, a, b, self._fresh)
@@ -388,7 +418,7 @@ class DistributedHessian:
                 done.record(main)
                 pb.side.wait_event(done)
                 with torch.cuda.stream(pb.side):
-                    pb.combine(self.hidden, a, b, channel=0)
+                    pb.combine(self.hidden, a, b, channel=0, mirror=not self._mirror_all)
         self._fresh = False
         self._tail = panels[-1]
         self._reduced = True
@@ -417,7 +447,11 @@ class DistributedHessian:
                 self._tail = (0, int(_lib.load().wush_hessian_tile_count(self.hidden)))
             else:
                 main.wait_stream(pb.side)       # the earlier panels are combined and mirrored
-            pb.combine(self.hidden, self._tail[0], self._tail[1], channel=1)
+            defer = getattr(self, "_mirror_all", False)
+            pb.combine(self.hidden, self._tail[0], self._tail[1], channel=1, mirror=not defer)
+            if defer:
+                pb.mirror(self.hidden, 0, int(_lib.load().wush_hessian_tile_count(self.hidden)), channel=1)
+                self._mirror_all = False
             self._tail = None
             self._reduced = True
             self._count = None                    # total is computed on demand (num_samples)
