@@ -781,7 +781,7 @@ def bench_block(args, dev, torch, dist, rank, world, barrier, peaks, peak_kind) 
     h = torch.randn(BLOCK_TOKENS, hs, generator=torch.Generator(device=dev).manual_seed(50 + rank), device=dev,
                     dtype=torch.float32).to(torch.bfloat16)
     h[:BLOCK_SEQ] = h_full0[:, rank * hs:(rank + 1) * hs]
-    blk = ShardedDecoderBlock(cfg, qw, transforms, gammas, BLOCK_SEQ, BLOCK_TOKENS, dev, micro_batches=2 if world > 1 else 1)
+    blk = ShardedDecoderBlock(cfg, qw, transforms, gammas, BLOCK_SEQ, BLOCK_TOKENS, dev, micro_batches=int(os.environ.get("WUSH_B200_BLOCK_MICRO_BATCHES", "2")) if world > 1 else 1)
 
     # ---- parity on sequence 0 (before the timed loop changes h) ---------------------------------------------
     first = blk.forward(h.clone())[:BLOCK_SEQ].float()
