@@ -428,7 +428,7 @@ def bench_decode(args, dev, torch, ops, peaks, peak_kind) -> dict:
                                    "successive calls read different weight copies (256 MB in rotation, twice the L2)"},
             "peak_kind": f"frac_hbm of {peak_kind} copy bandwidth (weights + activations + output once); frac_tensor of 4 x "
                          f"{peak_kind} bf16 burst",
-            "gpu_launches": sum(3 + 2 * (20 if m <= 1024 else 10) for _ in DECODE_SHAPES for m in DECODE_M),
+            "gpu_launches": sum(5 + (20 if m <= 1024 else 10) for _ in DECODE_SHAPES for m in DECODE_M),   # warm-ups + replayed graph
             "parity": _parity("decode", worst, 1e-2, "worst relative Frobenius error over the four (N,K) at M = 1 and 16, all "
                                                       "outputs vs the float64 oracle")}
 
