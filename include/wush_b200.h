@@ -289,6 +289,22 @@ WUSH_API int wush_hessian_peer_reduce(float* const* bufs, float* mc_buf, const i
                                       uint32_t* const* barrier_slots, uint32_t barrier_epoch, int* status, void* stream);
 
 /*
+ * One rank's piece of a buffer that exists on every GPU (symmetric memory) delivered to all of them in one launch:
+ * the exchange of FP4 codes + scale bytes between the ranks of a column-sharded decoder block (this build's
+ * multi-GPU form of the activation path of FPQuant4x16NoMasterFn.forward, inference_lib/src/fp_quant/module/
+ * linear_fns.py:494-539; the reference has no multi-GPU path of its own).
+ *
+ *   src     this rank's data, 16-byte aligned, `bytes` a multiple of 16
+ *   mc_dst  the multicast address of the destination range (every 16 bytes leave this GPU once, the NVSwitch writes
+ *           them into all ranks' buffers, this rank's included), or NULL
+ *   dst     when mc_dst is NULL: the destination addresses in the n_dst other ranks' buffers (HOST array of device
+ *           pointers, at most 16), written one after the other with plain peer stores
+ * The caller orders the stores against their readers (a barrier across the ranks after the launch).
+ */
+WUSH_API int wush_peer_broadcast(const void* src, void* mc_dst, void* const* dst, int n_dst, int64_t bytes,
+                                 void* stream);
+
+/*
  * Block-scaled FP4 GEMM, "TN":  y[m, n] (bf16) = alpha * deq(a)[m, k] . deq(b)[n, k]^T.
  *
  * Replace qutlass.matmul_mxf4_bf16_tn / qutlass.matmul_nvf4_bf16_tn as bound at

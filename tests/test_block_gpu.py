@@ -123,3 +123,23 @@ def test_two_gpu_block_matches_single_gpu_block(tmp_path):
     want = ShardedDecoderBlock(cfg, qw, transforms, gammas, SEQ, TOKENS, dev, micro_batches=1).forward(h.to(dev).clone())
     want = want.float().cpu().numpy()
     assert np.linalg.norm(got - want) <= 1e-2 * np.linalg.norm(want)
+
+
+def test_peer_broadcast_kernel_plain_stores_on_one_gpu():
+    """The one-launch delivery of a slot to several destination buffers, exercised with destinations on the same GPU
+    (the plain-store form; the multicast form needs an NVSwitch multicast address and is covered by the 2-GPU block
+    test with WUSH_B200_BLOCK_BROADCAST=1)."""
+    import ctypes
+    from wush_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    src = torch.randint(0, 256, (1 << 20) + 48, dtype=torch.uint8, device=dev)[:(1 << 20) + 32]
+    dsts = [torch.zeros_like(src) for _ in range(3)]
+    table = (ctypes.c_void_p * 3)(*[d.data_ptr() for d in dsts])
+    rc = lib.wush_peer_broadcast(src.data_ptr(), None, table, 3, src.numel(), torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert all(torch.equal(d, src) for d in dsts)
+    assert lib.wush_peer_broadcast(src.data_ptr(), None, table, 3, 24, None) == -2          # not a multiple of 16
+    assert lib.wush_peer_broadcast(src.data_ptr() + 4, None, table, 3, 32, None) == -3      # alignment
+    assert lib.wush_peer_broadcast(src.data_ptr(), None, table, 0, 32, None) == 0           # nobody to deliver to

@@ -61,6 +61,7 @@ def load() -> ctypes.CDLL:
         "wush_fused_quantize_nv": [vp, vp, i64, vp, vp, vp, i64, i32, i64, i64, i32, vp],
         "wush_fused_quantize_debug": [i32, vp, vp, i64, vp, vp, vp, i64, i32, vp, i64, i64, i32, vp],
         "wush_fused_quantize_strided": [i32, vp, i64, vp, i64, vp, vp, i64, vp, i64, i32, i64, vp, vp, i64, i64, i32, vp],
+        "wush_peer_broadcast": [vp, vp, vp, i32, i64, vp],
         "wush_row_sumsq": [vp, i64, vp, i64, i64, vp],
         "wush_swiglu": [vp, vp, i64, vp, i64, i64, i64, vp],
         "wush_sf_to_blocked": [vp, vp, i64, i64, vp],

@@ -226,3 +226,59 @@ extern "C" int wush_hessian_mirror_tiles(float* h, int64_t hidden, int64_t tile_
       h, hidden, nblk, tile_begin, items, rank, world, peer::RankBarrier{barrier_slots, barrier_epoch, status});
   return (int)cudaGetLastError();
 }
+
+// ---- one rank's slot of a symmetric buffer delivered to every rank in one launch ------------------------------
+namespace wush {
+namespace peer {
+
+struct BroadcastParams {
+  const uint4* src;              // this rank's data (its slot of its own buffer), 16-byte units
+  uint4* mc_dst;                 // the slot's multicast address (the switch replicates every store), or null
+  uint4* dst[kMaxWorld];         // else: the slot's address in every other rank's buffer
+  int n_dst;
+  int64_t units;
+};
+
+// With a multicast address every 16 bytes leave this GPU once (multimem.st) and the NVSwitch writes them into all
+// ranks' buffers; without, the kernel stores them to each peer in turn.
+__global__ void __launch_bounds__(256) peer_broadcast_kernel(const BroadcastParams p) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.units; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = p.src[i];
+    if (p.mc_dst != nullptr) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"l"(p.mc_dst + i),
+                   "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w))
+                   : "memory");
+    } else {
+      for (int r = 0; r < p.n_dst; ++r) p.dst[r][i] = v;
+    }
+  }
+}
+
+}  // namespace peer
+}  // namespace wush
+
+extern "C" int wush_peer_broadcast(const void* src, void* mc_dst, void* const* dst, int n_dst, int64_t bytes,
+                                   void* stream) {
+  using namespace wush;
+  if (!src || (!mc_dst && n_dst > 0 && !dst)) return WUSH_ERR_NULL_POINTER;
+  if (bytes < 0 || bytes % 16 != 0 || n_dst < 0 || n_dst > peer::kMaxWorld) return WUSH_ERR_BAD_SHAPE;
+  if (((uintptr_t)src & 15) || ((uintptr_t)mc_dst & 15)) return WUSH_ERR_BAD_ALIGNMENT;
+  if (bytes == 0 || (!mc_dst && n_dst == 0)) return WUSH_OK;
+  if (const int rc = require_sm100()) return rc;
+  peer::BroadcastParams p{};
+  p.src = (const uint4*)src;
+  p.mc_dst = (uint4*)mc_dst;
+  p.n_dst = mc_dst ? 0 : n_dst;
+  for (int r = 0; r < p.n_dst; ++r) {
+    if (!dst[r]) return WUSH_ERR_NULL_POINTER;
+    if ((uintptr_t)dst[r] & 15) return WUSH_ERR_BAD_ALIGNMENT;
+    p.dst[r] = (uint4*)dst[r];
+  }
+  p.units = bytes / 16;
+  int64_t blocks = (p.units + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 4;
+  if (blocks > cap) blocks = cap;
+  peer::peer_broadcast_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
+}
