@@ -111,11 +111,15 @@ def _worker(rank, world, port, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_block_matches_single_gpu_block(tmp_path):
+@pytest.mark.parametrize("broadcast", ["0", "1"])
+def test_two_gpu_block_matches_single_gpu_block(tmp_path, monkeypatch, broadcast):
+    """broadcast "0": slots travel as one device-to-device copy per peer; "1": by the one-launch broadcast kernel
+    (through the multicast address where the GPUs have one).  The spawned ranks inherit the environment."""
     import torch.multiprocessing as mp
     from wush_b200.block import ShardedDecoderBlock
+    monkeypatch.setenv("WUSH_B200_BLOCK_BROADCAST", broadcast)
     out = str(tmp_path / "h.npy")
-    mp.spawn(_worker, args=(2, 29950 + os.getpid() % 300, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29950 + (os.getpid() + int(broadcast) * 150) % 300, out), nprocs=2, join=True)
     got = np.load(out)
     dev = torch.device("cuda:0")
     cfg, qw, transforms, gammas, h = _setup("mx", dev)
