@@ -137,7 +137,7 @@ def test_peer_broadcast_kernel_plain_stores_on_one_gpu():
     from wush_b200 import _lib
     lib = _lib.load()
     dev = torch.device("cuda:0")
-    src = torch.randint(0, 256, (1 << 20) + 48, dtype=torch.uint8, device=dev)[:(1 << 20) + 32]
+    src = torch.randint(0, 256, ((1 << 20) + 48,), dtype=torch.uint8, device=dev)[:(1 << 20) + 32]
     dsts = [torch.zeros_like(src) for _ in range(3)]
     table = (ctypes.c_void_p * 3)(*[d.data_ptr() for d in dsts])
     rc = lib.wush_peer_broadcast(src.data_ptr(), None, table, 3, src.numel(), torch.cuda.current_stream(dev).cuda_stream)
