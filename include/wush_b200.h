@@ -317,7 +317,8 @@ WUSH_API int wush_peer_broadcast(const void* src, void* mc_dst, void* const* dst
  *              hold finite scale bytes (zero is fine)
  *   alpha      device pointer to one fp32 (1 / (weight_global_scale * act_global_scale) in the reference)
  *   y          bf16 [m, n] row-major, 16-byte aligned; n % 8 == 0, k % 128 == 0
- *   splits     0 = choose automatically.  m <= 4 (decode; WUSH_B200_GEMV_MAX_M lowers the limit, 0 switches it off):
+ *   splits     0 = choose automatically.  m <= 4 and k <= 8192 (decode; WUSH_B200_GEMV_MAX_M / _MAX_K move the limits, 0 rows
+ *              switches it off):
  *              a matrix-vector kernel streams the weight bytes once with plain loads and multiplies on the CUDA cores
  *              (exact fp16 sums of 8 products, fp32 from there on), 16 weight rows per CTA, no K splits.
  *              Otherwise, when few output tiles exist (small m: the GEMM streams the weights once and is bound by
